@@ -1,0 +1,362 @@
+// bf16 GEMM for sm_100a: tcgen05.mma with TMEM accumulators, TMA-fed operand
+// pipeline, persistent warp-specialised CTAs.
+//
+//   C[M,N] (+)= alpha * A[M,K] * B[N,K]^T (+ bias[N])
+//
+// A and B may each be K-major (contraction dimension contiguous) or MN-major
+// (the M/N dimension contiguous), which covers the three GEMMs of a linear
+// layer without a transposed weight copy:
+//   forward  Y  = X  * W^T      A = X  (K-major)   B = W  (K-major)
+//   dgrad    dX = dY * W        A = dY (K-major)   B = W  (MN-major)
+//   wgrad    dW += dY^T * X     A = dY (MN-major)  B = X  (MN-major), fp32 accumulate
+//
+// Roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and
+// TMEM owner, warps 2-5 = epilogue (TMEM -> registers -> global).  Two TMEM
+// accumulator buffers let the epilogue of tile i overlap the main loop of tile
+// i+1.  The library GEMM this replaces is cuBLAS behind nn.Linear in the
+// reference (opt_prime traced submodules call nn.Linear -> cuBLASLt).
+#include "sm100_common.cuh"
+
+namespace b200 {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_UMMA_K = 16;
+
+enum GemmFlags : int {
+  GEMM_OUT_F32 = 1,     // C is fp32 (else bf16)
+  GEMM_ACCUMULATE = 2,  // C += result (C must be fp32 or bf16 as per GEMM_OUT_F32)
+  GEMM_BIAS = 4,        // add bf16 bias[N]
+};
+
+struct GemmArgs {
+  void* C;
+  const __nv_bfloat16* bias;
+  int M, N, K;
+  long long ldc;
+  int a_mn, b_mn;
+  int flags;
+  float alpha;
+  int tiles_m, tiles_n;
+  int* err;
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + alignment slack
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  // Grouped rasterisation: 8 M-tiles share each B panel while it is L2-hot.
+  constexpr int GROUP = 8;
+  int per_group = GROUP * tiles_n;
+  int g = tile / per_group;
+  int first_m = g * GROUP;
+  int gsize = min(tiles_m - first_m, GROUP);
+  int r = tile - g * per_group;
+  tm = first_m + (r % gsize);
+  tn = r / gsize;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs p) {
+  using S = GemmSmem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + S::STAGES;
+  uint64_t* tmem_full = empty_bar + S::STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  __shared__ int cta_abort;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int nkb = (p.K + GEMM_BK - 1) / GEMM_BK;
+
+  if (threadIdx.x == 0) {
+    cta_abort = 0;
+    for (int s = 0; s < S::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 4);
+    }
+    fence_barrier_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int m0 = tm * GEMM_BM, n0 = tn * BN;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, p.err, ERR_WAIT_EMPTY, &cta_abort)) { ok = false; break; }
+          uint8_t* sA = smem + s * S::STAGE_BYTES;
+          uint8_t* sB = sA + S::A_BYTES;
+          mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
+          const int k0 = kb * GEMM_BK;
+          if (!p.a_mn) {
+            tma_load_2d(sA, &tmA, &full_bar[s], k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < GEMM_BM / 64; ++j) tma_load_2d(sA + j * 8192, &tmA, &full_bar[s], m0 + j * 64, k0);
+          }
+          if (!p.b_mn) {
+            tma_load_2d(sB, &tmB, &full_bar[s], k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sB + j * 8192, &tmB, &full_bar[s], n0 + j * 64, k0);
+          }
+          if (++s == S::STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+      if (!ok) {
+        // Error path: let copies already in flight land before the CTA exits.
+        for (int i = 0; i < S::STAGES; ++i) {
+          unsigned long long t0 = globaltimer_ns();
+          while (!mbar_try_wait(&full_bar[i], 0) && !mbar_try_wait(&full_bar[i], 1) && globaltimer_ns() - t0 < 1000000ull) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(GEMM_BM, BN, p.a_mn, p.b_mn);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int buf = it & 1;
+        if (!mbar_wait(&tmem_empty[buf], ((it >> 1) & 1) ^ 1, p.err, ERR_WAIT_TMEM_EMPTY, &cta_abort)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&full_bar[s], ph, p.err, ERR_WAIT_FULL, &cta_abort)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_base = smem_u32(smem + s * S::STAGE_BYTES);
+          const uint32_t b_base = a_base + S::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
+            const uint64_t adesc = p.a_mn ? make_smem_desc_sw128(a_base + k * 2048, 8192, 1024)
+                                          : make_smem_desc_sw128(a_base + k * 32, 16, 1024);
+            const uint64_t bdesc = p.b_mn ? make_smem_desc_sw128(b_base + k * 2048, 8192, 1024)
+                                          : make_smem_desc_sw128(b_base + k * 32, 16, 1024);
+            umma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
+          }
+          umma_commit(&empty_bar[s]);
+          if (++s == S::STAGES) { s = 0; ph ^= 1; }
+        }
+        if (ok) umma_commit(&tmem_full[buf]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    const bool out_f32 = p.flags & GEMM_OUT_F32;
+    const bool accum = p.flags & GEMM_ACCUMULATE;
+    const bool has_bias = p.flags & GEMM_BIAS;
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      const int buf = it & 1;
+      ok = mbar_wait(&tmem_full[buf], (it >> 1) & 1, p.err, ERR_WAIT_TMEM_FULL, &cta_abort);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row = tm * GEMM_BM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t t_row = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = tn * BN + c * 32;
+        if (row_ok && col0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+          if (has_bias) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
+          }
+          if (out_f32) {
+            float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              if (col0 + i < p.N) {  // N % 4 == 0 is required
+                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                if (accum) {
+                  float4 old = *reinterpret_cast<const float4*>(dst + i);
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *reinterpret_cast<float4*>(dst + i) = o;
+              }
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              if (col0 + i < p.N) {  // N % 8 == 0 is required
+                if (accum) {
+                  uint4 old = *reinterpret_cast<const uint4*>(dst + i);
+                  const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    float2 f = __bfloat1622float2(ob[j]);
+                    v[i + 2 * j] += f.x;
+                    v[i + 2 * j + 1] += f.y;
+                  }
+                }
+                uint4 o;
+                o.x = pack_bf16x2(v[i], v[i + 1]);
+                o.y = pack_bf16x2(v[i + 2], v[i + 3]);
+                o.z = pack_bf16x2(v[i + 4], v[i + 5]);
+                o.w = pack_bf16x2(v[i + 6], v[i + 7]);
+                *reinterpret_cast<uint4*>(dst + i) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess || !ptr) return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, row pitch `ld` elements.
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+static int g_num_sms = 0;
+
+template <int BN>
+static int launch_gemm(const void* A, const void* B, GemmArgs& p, long long lda, long long ldb, int max_ctas, cudaStream_t stream) {
+  using S = GemmSmem<BN>;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!p.a_mn) rc = make_tmap_bf16_2d(&tmA, A, p.K, p.M, lda, GEMM_BK, GEMM_BM);
+  else rc = make_tmap_bf16_2d(&tmA, A, p.M, p.K, lda, 64, GEMM_BK);
+  if (rc) return rc;
+  if (!p.b_mn) rc = make_tmap_bf16_2d(&tmB, B, p.K, p.N, ldb, GEMM_BK, BN);
+  else rc = make_tmap_bf16_2d(&tmB, B, p.N, p.K, ldb, 64, GEMM_BK);
+  if (rc) return rc;
+  p.tiles_m = (p.M + GEMM_BM - 1) / GEMM_BM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) return -3;
+    attr_set = true;
+  }
+  if (!g_num_sms) {
+    int dev;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  int ctas = g_num_sms;
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  int tiles = p.tiles_m * p.tiles_n;
+  if (tiles < ctas) ctas = tiles;
+  gemm_bf16_tcgen05_kernel<BN><<<ctas, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace b200
+
+// C[M,N] (+)= alpha * A * B^T (+ bias).  a_mn / b_mn: 0 = K-major ([rows][K], pitch ld), 1 = MN-major ([K][rows]).
+// Requirements: all base pointers 16-byte aligned; lda, ldb multiples of 8 elements; N % 8 == 0; ldc % 8 == 0
+// (bf16) or % 4 == 0 (fp32).  `err` is a device int that receives a nonzero code if a bounded wait ran out.
+// bn: 0 = pick, else 128 or 256.  max_ctas limits the persistent grid (0 = all SMs).
+extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                              long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int flags, float alpha,
+                              int bn, int max_ctas, int* err, cudaStream_t stream) {
+  using namespace b200;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (N % 8) || (ldc % 4) || (!(flags & GEMM_OUT_F32) && (ldc % 8))) return -10;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -11;
+  GemmArgs p;
+  p.C = C;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.M = M; p.N = N; p.K = K;
+  p.ldc = ldc;
+  p.a_mn = a_mn; p.b_mn = b_mn;
+  p.flags = flags;
+  p.alpha = alpha;
+  p.err = err;
+  if (bn == 0) {
+    // 256-wide tiles halve A re-reads; fall back to 128 when that fills the SMs better.
+    long long t256 = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256);
+    bn = (t256 >= 148 * 2 || (N % 256 == 0 && t256 >= 148)) ? 256 : 128;
+    if (N <= 128) bn = 128;
+  }
+  if (bn == 256) return launch_gemm<256>(A, B, p, lda, ldb, max_ctas, stream);
+  return launch_gemm<128>(A, B, p, lda, ldb, max_ctas, stream);
+}

@@ -1,0 +1,273 @@
+// RMSNorm / LayerNorm forward and backward for bf16 activations (fp32 math).
+//
+// One CTA per row in the forward; the backward is persistent (a fixed number
+// of CTAs stride over the rows) so that each CTA can keep its partial weight
+// (and bias) gradient in registers and spill it once to a [ctas, H] fp32
+// scratch that a second small kernel folds into the gradient.
+//
+// The forward optionally fuses the residual add that precedes every norm in a
+// pre-norm transformer block:  r = x + residual;  y = norm(r) * w.
+// Replaces eager HF norms of the reference's traced graphs (LlamaRMSNorm /
+// nn.LayerNorm, e.g. gpt-neox/megatron/model/norms.py:34-76).
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace b200 {
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_MAX_VEC = 4;  // 16-byte vectors per thread -> H <= 256*8*4 = 8192
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (l < NORM_THREADS / 32) ? red[l] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+struct Vec8 {
+  float f[8];
+};
+__device__ __forceinline__ Vec8 load8(const __nv_bfloat16* p) {
+  uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&u);
+  Vec8 v;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __bfloat1622float2(b[i]);
+    v.f[2 * i] = f.x;
+    v.f[2 * i + 1] = f.y;
+  }
+  return v;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const Vec8& v) {
+  uint4 u;
+  __nv_bfloat162* b = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) b[i] = __floats2bfloat162_rn(v.f[2 * i], v.f[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+// ------------------------------------------------------------------ forward
+// IS_LN: LayerNorm (mean subtraction, optional bias) else RMSNorm.
+template <bool IS_LN>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
+                const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b,
+                __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ res_out,
+                float* __restrict__ stat_rstd, float* __restrict__ stat_mean, int rows, int H, float eps) {
+  __shared__ float red[NORM_THREADS / 32];
+  const int row = blockIdx.x;
+  if (row >= rows) return;
+  const long long base = static_cast<long long>(row) * H;
+  const int nvec = H / 8;
+  Vec8 v[NORM_MAX_VEC];
+  float s = 0.f, ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    const int c = threadIdx.x + i * NORM_THREADS;
+    if (c < nvec) {
+      v[i] = load8(x + base + c * 8);
+      if (residual) {
+        Vec8 r = load8(residual + base + c * 8);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i].f[j] += r.f[j];
+      }
+      if (res_out) {
+        store8(res_out + base + c * 8, v[i]);
+        // norm the value that was stored (bf16-rounded), as the unfused graph would
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i].f[j] = __bfloat162float(__float2bfloat16(v[i].f[j]));
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { s += v[i].f[j]; ss += v[i].f[j] * v[i].f[j]; }
+    }
+  }
+  float mean = 0.f;
+  if (IS_LN) {
+    mean = block_sum(s, red) / H;
+    float var = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { float d = v[i].f[j] - mean; var += d * d; }
+      }
+    }
+    ss = block_sum(var, red);
+  } else {
+    ss = block_sum(ss, red);
+  }
+  const float rstd = rsqrtf(ss / H + eps);
+  if (threadIdx.x == 0) {
+    if (stat_rstd) stat_rstd[row] = rstd;
+    if (IS_LN && stat_mean) stat_mean[row] = mean;
+  }
+#pragma unroll
+  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    const int c = threadIdx.x + i * NORM_THREADS;
+    if (c < nvec) {
+      Vec8 wv = load8(w + c * 8);
+      Vec8 o;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o.f[j] = (v[i].f[j] - mean) * rstd * wv.f[j];
+      if (IS_LN && b) {
+        Vec8 bv = load8(b + c * 8);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o.f[j] += bv.f[j];
+      }
+      store8(y + base + c * 8, o);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ backward
+// dx = rstd * (g - xhat * mean(g * xhat) [- mean(g)])   with g = dy * w
+// dw partial = sum_rows dy * xhat ; db partial = sum_rows dy
+// `dres` (optional) is added to dx: the gradient arriving on the residual branch.
+template <bool IS_LN>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                const __nv_bfloat16* __restrict__ w, const float* __restrict__ stat_rstd,
+                const float* __restrict__ stat_mean, const __nv_bfloat16* __restrict__ dres,
+                __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, float* __restrict__ db_partial,
+                int rows, int H) {
+  __shared__ float red[NORM_THREADS / 32];
+  const int nvec = H / 8;
+  float dw_acc[NORM_MAX_VEC][8];
+  float db_acc[NORM_MAX_VEC][8];
+  Vec8 wv[NORM_MAX_VEC];
+#pragma unroll
+  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    const int c = threadIdx.x + i * NORM_THREADS;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { dw_acc[i][j] = 0.f; db_acc[i][j] = 0.f; wv[i].f[j] = 0.f; }
+    if (c < nvec) wv[i] = load8(w + c * 8);
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const long long base = static_cast<long long>(row) * H;
+    const float rstd = stat_rstd[row];
+    const float mean = IS_LN ? stat_mean[row] : 0.f;
+    Vec8 g[NORM_MAX_VEC], xh[NORM_MAX_VEC];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nvec) {
+        Vec8 d = load8(dy + base + c * 8);
+        Vec8 xv = load8(x + base + c * 8);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i].f[j] = (xv.f[j] - mean) * rstd;
+          g[i].f[j] = d.f[j] * wv[i].f[j];
+          dw_acc[i][j] += d.f[j] * xh[i].f[j];
+          if (IS_LN) db_acc[i][j] += d.f[j];
+          s1 += g[i].f[j] * xh[i].f[j];
+          s2 += g[i].f[j];
+        }
+      }
+    }
+    s1 = block_sum(s1, red) / H;
+    if (IS_LN) s2 = block_sum(s2, red) / H; else s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nvec) {
+        Vec8 o;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o.f[j] = rstd * (g[i].f[j] - xh[i].f[j] * s1 - s2);
+        if (dres) {
+          Vec8 r = load8(dres + base + c * 8);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o.f[j] += r.f[j];
+        }
+        store8(dx + base + c * 8, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    const int c = threadIdx.x + i * NORM_THREADS;
+    if (c < nvec) {
+      float* dst = dw_partial + static_cast<long long>(blockIdx.x) * H + c * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dst[j] = dw_acc[i][j];
+      if (IS_LN && db_partial) {
+        float* dstb = db_partial + static_cast<long long>(blockIdx.x) * H + c * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dstb[j] = db_acc[i][j];
+      }
+    }
+  }
+}
+
+// Fold [parts, H] partials into grad (fp32, accumulate) or grad_bf16 (overwrite or accumulate).
+__global__ void norm_fold_partials_kernel(const float* __restrict__ partial, int parts, int H,
+                                          float* __restrict__ grad_f32, __nv_bfloat16* __restrict__ grad_bf16,
+                                          int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  float s = 0.f;
+  for (int p = 0; p < parts; ++p) s += partial[static_cast<long long>(p) * H + c];
+  if (grad_f32) grad_f32[c] = accumulate ? grad_f32[c] + s : s;
+  if (grad_bf16) grad_bf16[c] = __float2bfloat16(accumulate ? __bfloat162float(grad_bf16[c]) + s : s);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_norm_bwd_ctas() { return 296; }
+
+// y = norm(x [+ residual]) * w [+ b]; res_out (optional) receives x + residual.  H % 8 == 0, H <= 8192.
+extern "C" int b200_norm_fwd(const void* x, const void* residual, const void* w, const void* b, void* y, void* res_out,
+                             float* rstd, float* mean, int rows, int H, float eps, int is_layernorm,
+                             cudaStream_t stream) {
+  if (H % 8 || H > NORM_THREADS * 8 * NORM_MAX_VEC) return -10;
+  if (rows <= 0) return 0;
+  auto X = static_cast<const __nv_bfloat16*>(x);
+  auto R = static_cast<const __nv_bfloat16*>(residual);
+  auto W = static_cast<const __nv_bfloat16*>(w);
+  auto B = static_cast<const __nv_bfloat16*>(b);
+  auto Y = static_cast<__nv_bfloat16*>(y);
+  auto RO = static_cast<__nv_bfloat16*>(res_out);
+  if (is_layernorm) norm_fwd_kernel<true><<<rows, NORM_THREADS, 0, stream>>>(X, R, W, B, Y, RO, rstd, mean, rows, H, eps);
+  else norm_fwd_kernel<false><<<rows, NORM_THREADS, 0, stream>>>(X, R, W, B, Y, RO, rstd, mean, rows, H, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Backward.  `scratch` holds 2 * ctas * H floats (ctas = b200_norm_bwd_ctas()).
+// dw/db go to fp32 (dw_f32/db_f32, accumulate flag) and/or bf16 buffers.
+extern "C" int b200_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const float* mean,
+                             const void* dres, void* dx, float* scratch, float* dw_f32, void* dw_bf16, float* db_f32,
+                             void* db_bf16, int accumulate, int rows, int H, int is_layernorm, cudaStream_t stream) {
+  if (H % 8 || H > NORM_THREADS * 8 * NORM_MAX_VEC) return -10;
+  if (rows <= 0) return 0;
+  int ctas = b200_norm_bwd_ctas();
+  if (ctas > rows) ctas = rows;
+  float* dwp = scratch;
+  float* dbp = scratch + static_cast<long long>(b200_norm_bwd_ctas()) * H;
+  auto DY = static_cast<const __nv_bfloat16*>(dy);
+  auto X = static_cast<const __nv_bfloat16*>(x);
+  auto W = static_cast<const __nv_bfloat16*>(w);
+  auto DR = static_cast<const __nv_bfloat16*>(dres);
+  auto DX = static_cast<__nv_bfloat16*>(dx);
+  if (is_layernorm) norm_bwd_kernel<true><<<ctas, NORM_THREADS, 0, stream>>>(DY, X, W, rstd, mean, DR, DX, dwp, dbp, rows, H);
+  else norm_bwd_kernel<false><<<ctas, NORM_THREADS, 0, stream>>>(DY, X, W, rstd, mean, DR, DX, dwp, nullptr, rows, H);
+  const int t = 256;
+  norm_fold_partials_kernel<<<(H + t - 1) / t, t, 0, stream>>>(dwp, ctas, H, dw_f32, static_cast<__nv_bfloat16*>(dw_bf16), accumulate);
+  if (is_layernorm && (db_f32 || db_bf16))
+    norm_fold_partials_kernel<<<(H + t - 1) / t, t, 0, stream>>>(dbp, ctas, H, db_f32, static_cast<__nv_bfloat16*>(db_bf16), accumulate);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

@@ -1,0 +1,78 @@
+"""Device-timed micro-benchmarks of the sm_100a kernels against their library counterparts.
+
+``python -m aicomp_b200.ops.microbench gemm`` times the tcgen05 GEMM and
+``torch.matmul`` (cuBLAS) on the linear-layer shapes of Llama-3-8B with CUDA
+events, L2 flushed between iterations, and prints one JSON line per shape.
+"""
+from __future__ import annotations
+
+import json
+import sys
+
+import torch
+
+from aicomp_b200 import ops
+
+
+def _time(fn, iters=10, warmup=3, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def bench_gemm(shapes=None):
+    dev = "cuda"
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    shapes = shapes or [
+        # (M, N, K, a_mn, b_mn, out_f32_accumulate, label)
+        (2048, 6144, 4096, False, False, False, "qkv fwd"),
+        (2048, 4096, 4096, False, False, False, "o_proj fwd"),
+        (2048, 28672, 4096, False, False, False, "gate_up fwd"),
+        (2048, 4096, 14336, False, False, False, "down fwd"),
+        (2048, 4096, 28672, False, True, False, "gate_up dgrad"),
+        (28672, 4096, 2048, True, True, True, "gate_up wgrad"),
+        (4096, 14336, 2048, True, True, True, "down wgrad"),
+        (8192, 8192, 8192, False, False, False, "square 8k"),
+        (2048, 128256, 4096, False, False, False, "lm_head fwd"),
+    ]
+    for (M, N, K, a_mn, b_mn, acc, label) in shapes:
+        a = torch.randn((K, M) if a_mn else (M, K), device=dev, dtype=torch.bfloat16)
+        b = torch.randn((K, N) if b_mn else (N, K), device=dev, dtype=torch.bfloat16)
+        out = torch.zeros(M, N, device=dev, dtype=torch.float32 if acc else torch.bfloat16)
+        res = {"shape": [M, N, K], "label": label, "a_mn": a_mn, "b_mn": b_mn}
+        flops = 2.0 * M * N * K
+        for bn in (128, 256):
+            t = _time(lambda: ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, accumulate=acc, bn=bn), flush=flush)
+            res[f"ours_bn{bn}_ms"] = round(t, 4)
+            res[f"ours_bn{bn}_tflops"] = round(flops / t / 1e9, 1)
+        A = a.t() if a_mn else a
+        B = b if b_mn else b.t()
+        if acc:
+            t = _time(lambda: out.addmm_(A.float() if False else A, B) if out.dtype == torch.bfloat16 else torch.matmul(A, B), flush=flush)
+        else:
+            t = _time(lambda: torch.matmul(A, B, out=out), flush=flush)
+        res["cublas_ms"] = round(t, 4)
+        res["cublas_tflops"] = round(flops / t / 1e9, 1)
+        ops.check_errors()
+        print(json.dumps(res), flush=True)
+        del a, b, out
+
+
+if __name__ == "__main__":
+    what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
+    if what == "gemm":
+        bench_gemm()
+    else:
+        raise SystemExit(f"unknown benchmark {what}")
