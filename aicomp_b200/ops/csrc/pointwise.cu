@@ -192,7 +192,7 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __rest
   }
   // block reduce (max, sum)
   float wm = warp_max(m);
-  s *= __expf(m - wm);
+  s = (m == -CUDART_INF_F) ? 0.f : s * __expf(m - wm);  // idle threads hold (-inf, 0)
   s = warp_add(s);
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
   if (l == 0) { red_m[w] = wm; red_s[w] = s; }
@@ -201,7 +201,7 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __rest
     float mm = (l < CE_THREADS / 32) ? red_m[l] : -CUDART_INF_F;
     float ssum = (l < CE_THREADS / 32) ? red_s[l] : 0.f;
     const float gm = warp_max(mm);
-    ssum *= __expf(mm - gm);
+    ssum = (mm == -CUDART_INF_F) ? 0.f : ssum * __expf(mm - gm);
     ssum = warp_add(ssum);
     if (l == 0) { sh_max = gm; sh_lse = gm + logf(ssum); }
   }
