@@ -401,10 +401,13 @@ def trace_model(model: nn.Module, input_names: Optional[Sequence[str]] = None,
             ckw.setdefault("return_dict", True)
 
     examples = dict(example_inputs or {})
+    symbolic_only = False
     for n in input_names:
         if n not in examples:
             if model_type == MODEL_TYPE_SYMBOLIC:
-                raise ValueError("example_inputs are required for plain nn.Module models")
+                # plain modules without examples: classic symbolic trace (no shape-dependent control flow allowed)
+                symbolic_only = True
+                break
             examples[n] = _default_example(model, n, example_batch, example_seq)
     examples = {k: _to_meta(v) for k, v in examples.items()}
 
@@ -429,6 +432,7 @@ def trace_model(model: nn.Module, input_names: Optional[Sequence[str]] = None,
 
     tracer = MetaTracer(leaf_classes=leaf_classes, leaf_predicate=leaf_predicate)
     tracer._strip_prefix = "_m."
+    tracer._meta_enabled = not symbolic_only
 
     # placeholders get their meta value from the examples
     orig_create_proxy = tracer.create_proxy

@@ -45,6 +45,12 @@ class _TensorSlot:
     def __init__(self, index: int):
         self.index = index
 
+    def __eq__(self, other):
+        return isinstance(other, _TensorSlot) and other.index == self.index
+
+    def __hash__(self):
+        return hash(("slot", self.index))
+
 
 @dataclass
 class _Header:

@@ -1,0 +1,69 @@
+"""PP / DP / TP training over gloo on CPU must reproduce a single-process eager run."""
+import pytest
+
+from tests.dist_utils import run_workers
+from tests.models_small import reference_losses
+
+
+def _check(results, ref_losses, ref_checksum, rtol=2e-4):
+    last = [r for r in results if r["losses"][0] is not None]
+    assert last, "no rank reported losses"
+    for r in last[:1]:
+        for got, ref in zip(r["losses"], ref_losses):
+            assert abs(got - ref) <= rtol * abs(ref) + 1e-5, (r["losses"], ref_losses)
+
+
+@pytest.mark.parametrize("model", ["gpt2", "llama", "mlp"])
+@pytest.mark.parametrize("mode", ["gpipe", "1f1b"])
+def test_pp2_matches_eager(model, mode):
+    ref, cs = reference_losses(model, steps=3, batch=4, num_mb=2)
+    res = run_workers("train_worker", 2, {"model": model, "pp": 2, "num_mb": 2, "mode": mode, "steps": 3, "batch": 4})
+    _check(res, ref, cs)
+    total = sum(r["checksum"] for r in res)
+    assert abs(total - cs) <= 1e-4 * cs
+
+
+def test_pp4_1f1b_four_microbatches():
+    ref, cs = reference_losses("gpt2", steps=2, batch=8, num_mb=4)
+    res = run_workers("train_worker", 4, {"model": "gpt2", "pp": 4, "num_mb": 4, "mode": "1f1b", "steps": 2, "batch": 8})
+    _check(res, ref, cs)
+
+
+def test_pp2_activation_checkpointing():
+    ref, cs = reference_losses("llama", steps=2, batch=4, num_mb=2)
+    res = run_workers("train_worker", 2, {"model": "llama", "pp": 2, "num_mb": 2, "steps": 2, "batch": 4, "act_ckpt": True})
+    _check(res, ref, cs)
+
+
+def test_dp2_averages_gradients():
+    ref, cs = reference_losses("gpt2", steps=3, batch=8, num_mb=2, dp=2)
+    res = run_workers("train_worker", 2, {"model": "gpt2", "dp": 2, "pp": 1, "num_mb": 2, "steps": 3, "batch": 8})
+    # each replica reports the mean loss of its own half; their mean is the reference's
+    for step in range(3):
+        got = sum(r["losses"][step] for r in res) / 2
+        assert abs(got - ref[step]) <= 2e-4 * abs(ref[step])
+    assert abs(res[0]["checksum"] - res[1]["checksum"]) <= 1e-9 * cs
+    assert abs(res[0]["checksum"] - cs) <= 1e-4 * cs
+
+
+@pytest.mark.parametrize("sp", [False, True])
+def test_tp2_llama_matches_eager(sp):
+    ref, cs = reference_losses("llama", steps=3, batch=4, num_mb=2)
+    res = run_workers("train_worker", 2, {"model": "llama", "tp": 2, "pp": 1, "num_mb": 2, "steps": 3, "batch": 4, "sp": sp})
+    _check(res, ref, cs, rtol=5e-4)
+
+
+def test_pp2_tp2_dp2_llama_3d():
+    ref, cs = reference_losses("llama", steps=2, batch=8, num_mb=2, dp=2)
+    res = run_workers("train_worker", 8, {"model": "llama", "tp": 2, "pp": 2, "dp": 2, "num_mb": 2, "steps": 2, "batch": 8},
+                      timeout=400)
+    last = [r for r in res if r["losses"][0] is not None]
+    for step in range(2):
+        got = sum(r["losses"][step] for r in last) / len(last)
+        assert abs(got - ref[step]) <= 5e-4 * abs(ref[step])
+
+
+def test_single_mode_broadcasts_assignment():
+    ref, cs = reference_losses("gpt2", steps=2, batch=4, num_mb=2)
+    res = run_workers("train_worker", 2, {"model": "gpt2", "pp": 2, "num_mb": 2, "steps": 2, "batch": 4, "ir": "SINGLE"})
+    _check(res, ref, cs)
