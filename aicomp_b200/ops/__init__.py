@@ -123,12 +123,14 @@ class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias):
         x2 = _rows(x)
-        y = gemm(x2, w, bias=bias)
+        # allocate with the final shape: a view made inside a Function may not be modified in place later (RoPE does)
+        y = torch.empty(*x.shape[:-1], w.shape[0], dtype=x.dtype, device=x.device)
+        gemm(x2, w, bias=bias, out=y.view(-1, w.shape[0]))
         ctx.save_for_backward(x2, w)
         ctx.has_bias = bias is not None
         ctx.x_shape = x.shape
         ctx.w_ref = w
-        return y.view(*x.shape[:-1], w.shape[0])
+        return y
 
     @staticmethod
     def backward(ctx, dy):
@@ -136,7 +138,8 @@ class _LinearFn(torch.autograd.Function):
         dy2 = _rows(dy)
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
-            dx = gemm(dy2, w, b_mn=True).view(ctx.x_shape)
+            dx = torch.empty(ctx.x_shape, dtype=dy.dtype, device=dy.device)
+            gemm(dy2, w, b_mn=True, out=dx.view(-1, w.shape[1]))
         if ctx.needs_input_grad[1]:
             mg = getattr(ctx.w_ref, "main_grad", None)
             if mg is not None:
@@ -183,8 +186,8 @@ class _NormFn(torch.autograd.Function):
             r2 = residual.reshape(-1, H)
             if not r2.is_contiguous():
                 r2 = r2.contiguous()
-        y = torch.empty_like(x2)
-        res_out = torch.empty_like(x2) if residual is not None else None
+        y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        res_out = torch.empty(x.shape, dtype=x.dtype, device=x.device) if residual is not None else None
         rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
         mean = torch.empty(rows, dtype=torch.float32, device=x.device) if is_ln else None
         lib = _lib.require()
@@ -192,15 +195,13 @@ class _NormFn(torch.autograd.Function):
                                rstd.data_ptr(), _lib.ptr(mean), rows, H, float(eps), int(is_ln), _lib.stream_ptr())
         _lib.check_rc(rc, "norm_fwd")
         _count()
-        ctx.save_for_backward(res_out if res_out is not None else x2, w, rstd, mean)
+        ctx.save_for_backward(res_out.view(-1, H) if res_out is not None else x2, w, rstd, mean)
         ctx.is_ln = is_ln
         ctx.has_res = residual is not None
         ctx.has_b = b is not None
         ctx.shape = x.shape
         ctx.w_ref, ctx.b_ref = w, b
-        if residual is not None:
-            return y.view(x.shape), res_out.view(x.shape)
-        return y.view(x.shape), None
+        return y, res_out
 
     @staticmethod
     def backward(ctx, dy, dres):
@@ -215,7 +216,7 @@ class _NormFn(torch.autograd.Function):
             dres2 = dres.reshape(-1, H)
             if not dres2.is_contiguous():
                 dres2 = dres2.contiguous()
-        dx = torch.empty_like(xin)
+        dx = torch.empty(ctx.shape, dtype=xin.dtype, device=xin.device)
         lib = _lib.require()
         scratch = _norm_scratch_for(xin.device, H)
         w_mg = getattr(ctx.w_ref, "main_grad", None)
@@ -232,8 +233,7 @@ class _NormFn(torch.autograd.Function):
         _count(3 if ctx.is_ln and ctx.has_b else 2)
         if w_mg is not None:
             ctx.w_ref.grad_accumulated = True
-        dxv = dx.view(ctx.shape)
-        return dxv, (dxv if ctx.has_res else None), dw, db, None, None
+        return dx, (dx if ctx.has_res else None), dw, db, None, None
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6, residual: Optional[torch.Tensor] = None
@@ -330,13 +330,13 @@ class _SwiGLUFn(torch.autograd.Function):
         g2 = gu.reshape(-1, 2 * I)
         if not g2.is_contiguous():
             g2 = g2.contiguous()
-        out = torch.empty(g2.shape[0], I, dtype=gu.dtype, device=gu.device)
+        out = torch.empty(*gu.shape[:-1], I, dtype=gu.dtype, device=gu.device)
         lib = _lib.require()
         _lib.check_rc(lib.b200_swiglu_fwd(g2.data_ptr(), out.data_ptr(), g2.shape[0], I, _lib.stream_ptr()), "swiglu_fwd")
         _count()
         ctx.save_for_backward(g2)
         ctx.shape = gu.shape
-        return out.view(*gu.shape[:-1], I)
+        return out
 
     @staticmethod
     def backward(ctx, dout):
@@ -345,11 +345,11 @@ class _SwiGLUFn(torch.autograd.Function):
         d2 = dout.reshape(-1, I)
         if not d2.is_contiguous():
             d2 = d2.contiguous()
-        dgu = torch.empty_like(g2)
+        dgu = torch.empty(ctx.shape, dtype=g2.dtype, device=g2.device)
         lib = _lib.require()
         _lib.check_rc(lib.b200_swiglu_bwd(g2.data_ptr(), d2.data_ptr(), dgu.data_ptr(), g2.shape[0], I, _lib.stream_ptr()), "swiglu_bwd")
         _count()
-        return dgu.view(ctx.shape)
+        return dgu
 
 
 def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
@@ -437,14 +437,14 @@ class _EmbeddingFn(torch.autograd.Function):
     def forward(ctx, ids, table):
         idc = ids.reshape(-1).long().contiguous()
         H = table.shape[1]
-        out = torch.empty(idc.numel(), H, dtype=table.dtype, device=table.device)
+        out = torch.empty(*ids.shape, H, dtype=table.dtype, device=table.device)
         lib = _lib.require()
         _lib.check_rc(lib.b200_embedding_fwd(idc.data_ptr(), table.data_ptr(), out.data_ptr(), idc.numel(), H, table.shape[0],
                                              _lib.stream_ptr()), "embedding_fwd")
         _count()
         ctx.save_for_backward(idc)
         ctx.t_ref = table
-        return out.view(*ids.shape, H)
+        return out
 
     @staticmethod
     def backward(ctx, dout):

@@ -53,6 +53,9 @@ class GradReducer:
         return p.grad
 
     def reduce(self) -> None:
+        pre = getattr(self, "pre_reduce", None)
+        if pre is not None:
+            pre()
         arena = getattr(self, "arena_grad", None)
         if arena is not None:  # contiguous fp32 gradient arena (FusedAdamW): reduce it in place, bucket by bucket
             n = arena.numel()
