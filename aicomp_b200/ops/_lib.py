@@ -63,6 +63,12 @@ def _bind(lib: ctypes.CDLL) -> None:
         fn.restype = c_int
 
 
+def rebind() -> None:
+    """Bind entry points registered in ``OPTIONAL_PROTOS`` after the library was loaded."""
+    if _lib is not None:
+        _bind(_lib)
+
+
 def load(required: bool = False) -> Optional[ctypes.CDLL]:
     """Load (building first if the sources changed and nvcc is present)."""
     global _lib, _load_error

@@ -104,6 +104,13 @@ class FusedAdamW(torch.optim.Optimizer):
     def attach_to_reducer(self, reducer) -> None:
         """Let a data-parallel ``GradReducer`` reduce the contiguous gradient arena in place."""
         if self.fused and reducer is not None:
+            fused = getattr(reducer, "_fused", None)
+            if fused is not None:  # move the gradient arena into peer-mapped memory (collective over the DP group)
+                new = fused.alloc_arena(self.total)
+                new.copy_(self.grad)
+                self.grad = new
+                for p, o in zip(self._order, self.offsets):
+                    p.main_grad = self.grad[o:o + p.numel()].view(p.shape)
             reducer.arena_grad = self.grad
             reducer.pre_reduce = self._fold_param_grads
 

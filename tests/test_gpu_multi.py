@@ -1,0 +1,33 @@
+"""Multi-GPU tests (2+ GPUs on one box, NCCL + peer memory).  Skipped when fewer GPUs are visible."""
+import pytest
+import torch
+
+from tests.dist_utils import run_workers
+
+pytestmark = pytest.mark.gpu
+
+
+def _need(n):
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+def test_fused_allreduce_and_kv_push_2gpu():
+    _need(2)
+    res = run_workers("gpu_collectives_worker", 2, {"tests": ["allreduce", "kv_push"]}, timeout=300,
+                      env_extra={"NCCL_NVLS_ENABLE": "0"})
+    for r in res:
+        assert r["allreduce"]["max_err"] < 1e-5, r
+        assert r["kv_push"]["ok"], r
+    print(res[0])
+
+
+def test_pp2_dp2_training_matches_across_backends():
+    _need(4)
+    base = {"model": "llama", "pp": 2, "dp": 2, "num_mb": 2, "steps": 3, "batch": 8, "use_gpu": True, "dtype": "bfloat16"}
+    a = run_workers("train_worker", 4, dict(base, dp_backend="nccl"), timeout=300, env_extra={"NCCL_NVLS_ENABLE": "0"})
+    b = run_workers("train_worker", 4, dict(base, dp_backend="fused"), timeout=300, env_extra={"NCCL_NVLS_ENABLE": "0"})
+    la = [r["losses"] for r in a if r["losses"][0] is not None][0]
+    lb = [r["losses"] for r in b if r["losses"][0] is not None][0]
+    for x, y in zip(la, lb):
+        assert abs(x - y) < 2e-2 * abs(x)
