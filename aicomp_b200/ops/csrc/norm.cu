@@ -271,3 +271,51 @@ extern "C" int b200_norm_bwd(const void* dy, const void* x, const void* w, const
     norm_fold_partials_kernel<<<(H + t - 1) / t, t, 0, stream>>>(dbp, ctas, H, db_f32, static_cast<__nv_bfloat16*>(db_bf16), accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+// ---------------------------------------------------------------- allocation-free RMSNorm backward
+#include "b200_noalloc.h"
+#include <mutex>
+
+// Partial weight gradients of b200_rmsnorm_bwd_noalloc: one row of H floats per CTA.  In host code this name is only
+// a handle for cudaGetSymbolAddress; kernels receive the looked-up device address.
+static __device__ __align__(256) float g_rmsnorm_noalloc_partials[B200_NOALLOC_CTAS * B200_NOALLOC_MAX_H];
+
+static int noalloc_scratch_for_current_device(float** out) {
+  constexpr int kMaxDevices = 64;
+  static float* cached[kMaxDevices] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200_NOALLOC_ERR_SYMBOL;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[dev]) {
+    void* p = nullptr;  // once per device, with that device current: the array has one instance per GPU
+    if (cudaGetSymbolAddress(&p, g_rmsnorm_noalloc_partials) != cudaSuccess || !p) return B200_NOALLOC_ERR_SYMBOL;
+    cached[dev] = static_cast<float*>(p);
+  }
+  *out = cached[dev];
+  return 0;
+}
+
+extern "C" int b200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
+                                        void* dx, float* dw_f32, void* dw_bf16, int accumulate, int rows, int H,
+                                        cudaStream_t stream) {
+  if (H > B200_NOALLOC_MAX_H) return B200_NOALLOC_ERR_TOO_LARGE;
+  if (H % 8 || H <= 0) return -10;
+  if (rows <= 0) return 0;
+  float* partials = nullptr;
+  int rc = noalloc_scratch_for_current_device(&partials);
+  if (rc) return rc;
+  int ctas = B200_NOALLOC_CTAS;
+  if (ctas > rows) ctas = rows;
+  // every CTA writes all H entries of its own row of `partials`, and the fold below reads exactly `ctas` rows:
+  // nothing left over from an earlier call is ever read, so no clearing is needed.
+  norm_bwd_kernel<false><<<ctas, NORM_THREADS, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), rstd,
+      nullptr, static_cast<const __nv_bfloat16*>(dres), static_cast<__nv_bfloat16*>(dx), partials, nullptr, rows, H);
+  if (dw_f32 || dw_bf16) {
+    const int t = 256;
+    norm_fold_partials_kernel<<<(H + t - 1) / t, t, 0, stream>>>(partials, ctas, H, dw_f32, static_cast<__nv_bfloat16*>(dw_bf16),
+                                                                  accumulate);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
