@@ -185,7 +185,7 @@ class Optimus_p:
             return self._user_loss_fn(model_out, labels)
         if self.model_type in (MODEL_TYPE_HF, MODEL_TYPE_VIT):
             logits = model_out["logits"] if isinstance(model_out, dict) else (model_out[0] if isinstance(model_out, (tuple, list)) else model_out)
-            return ops.cross_entropy(logits.reshape(-1, logits.shape[-1]), labels.reshape(-1), self.ignore_index)
+            return ops.cross_entropy(logits.reshape(-1, logits.shape[-1]), labels.reshape(-1), self.ignore_index, unit_grad=True)
         out = model_out[0] if isinstance(model_out, (tuple, list)) else model_out
         return F.mse_loss(out, labels)
 

@@ -393,7 +393,7 @@ class _CrossEntropyFn(torch.autograd.Function):
     """Mean token cross entropy; the logits buffer is overwritten by its own gradient in the forward."""
 
     @staticmethod
-    def forward(ctx, logits, labels, ignore_index):
+    def forward(ctx, logits, labels, ignore_index, unit_grad):
         V = logits.shape[-1]
         l2 = logits.reshape(-1, V)
         if l2.stride(-1) != 1:
@@ -407,28 +407,34 @@ class _CrossEntropyFn(torch.autograd.Function):
         loss_rows = torch.empty(rows, dtype=torch.float32, device=logits.device)
         need_grad = logits.requires_grad
         lib = _lib.require()
+        inv = (1.0 / n_valid).reshape(1)
         rc = lib.b200_cross_entropy(l2.data_ptr(), lab.data_ptr(), loss_rows.data_ptr(), rows, V, l2.stride(0), int(ignore_index),
-                                    1.0, int(need_grad), _lib.stream_ptr())
+                                    1.0, inv.data_ptr(), int(need_grad), _lib.stream_ptr())
         _lib.check_rc(rc, "cross_entropy")
         _count()
         if need_grad:
-            ctx.save_for_backward(l2, n_valid)
+            ctx.save_for_backward(l2)
             ctx.shape = logits.shape
-        return loss_rows.sum() / n_valid
+            ctx.unit_grad = unit_grad
+        return loss_rows.sum() * inv[0]
 
     @staticmethod
     def backward(ctx, dloss):
-        l2, n_valid = ctx.saved_tensors
-        l2.mul_((dloss / n_valid).to(l2.dtype))
-        return l2.view(ctx.shape), None, None
+        (l2,) = ctx.saved_tensors
+        if not ctx.unit_grad:  # the stored gradient is already d(mean loss)/d(logits); scale by the incoming gradient
+            l2.mul_(dloss.to(l2.dtype))
+        return l2.view(ctx.shape), None, None, None
 
 
-def cross_entropy(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
-    """Mean cross entropy over non-ignored tokens (fp32 math).  On the kernel path ``logits`` is consumed."""
+def cross_entropy(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100, unit_grad: bool = False) -> torch.Tensor:
+    """Mean cross entropy over non-ignored tokens (fp32 math).  On the kernel path ``logits`` is consumed.
+
+    ``unit_grad=True`` promises that ``backward`` starts from this loss with gradient 1 (what the pipeline
+    schedules do), which saves a pass over the vocabulary-sized gradient."""
     V = logits.shape[-1]
     if not kernels_for(logits) or V % 8:
         return F.cross_entropy(logits.reshape(-1, V).float(), labels.reshape(-1).long(), ignore_index=ignore_index)
-    return _CrossEntropyFn.apply(logits, labels, ignore_index)
+    return _CrossEntropyFn.apply(logits, labels, ignore_index, unit_grad)
 
 
 # ---------------------------------------------------------------------- embedding

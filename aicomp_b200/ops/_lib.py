@@ -36,7 +36,7 @@ _PROTOS = {
     "b200_swiglu_bwd": [P, P, P, L, I, P],
     "b200_gelu_fwd": [P, P, L, P],
     "b200_gelu_bwd": [P, P, P, L, P],
-    "b200_cross_entropy": [P, P, P, L, I, L, I, F, I, P],
+    "b200_cross_entropy": [P, P, P, L, I, L, I, F, P, I, P],
     "b200_embedding_fwd": [P, P, P, L, I, I, P],
     "b200_embedding_bwd": [P, P, P, L, I, I, P],
     "b200_softmax_fwd": [P, P, P, L, I, I, F, I, I, I, P],

@@ -48,7 +48,9 @@ struct GemmSmem {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
   static constexpr int B_BYTES = BN * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;   // 1024-aligned
+  static constexpr int EPI_BUF_BYTES = 32 * 128;            // 32 rows x 128 B
+  static constexpr int BAR_OFFSET = EPI_OFFSET + 4 * 2 * EPI_BUF_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + alignment slack
 };
 
@@ -66,7 +68,8 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 
 template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs p) {
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const __grid_constant__ CUtensorMap tmC, GemmArgs p) {
   using S = GemmSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -95,6 +98,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     fence_barrier_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
+    prefetch_tmap(&tmC);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 2 * BN);
@@ -179,10 +183,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     __syncwarp();
   } else {
     // ------------------------------------------------ epilogue (warps 2..5)
+    // TMEM -> registers -> (alpha, bias, cast) -> 128B-swizzled smem staging -> TMA store, or TMA reduce-add for
+    // fp32 accumulation (the add happens in the memory system: C is never read back into the SM).
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     const bool out_f32 = p.flags & GEMM_OUT_F32;
     const bool accum = p.flags & GEMM_ACCUMULATE;
     const bool has_bias = p.flags & GEMM_BIAS;
+    uint8_t* stage_base = smem + S::EPI_OFFSET + (warp - 2) * 2 * S::EPI_BUF_BYTES;
+    int sbuf = 0;
     int it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
@@ -193,60 +201,63 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      const int row = tm * GEMM_BM + q * 32 + lane;
-      const bool row_ok = row < p.M;
+      const int row0 = tm * GEMM_BM + q * 32;
       const uint32_t t_row = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
+      const int sw = lane & 7;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(t_row + c * 32, r);
         tmem_ld_wait();
         const int col0 = tn * BN + c * 32;
-        if (row_ok && col0 < p.N) {
-          float v[32];
+        if (col0 >= p.N) continue;  // warp-uniform: the whole chunk is outside C
+        float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-          if (has_bias) {
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+        if (has_bias) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
+          for (int i = 0; i < 32; ++i)
+            if (col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
+        }
+        uint8_t* sb = stage_base + sbuf * S::EPI_BUF_BYTES;
+        if (out_f32) {
+          if (lane == 0) tma_store_wait_read<1>();  // the store issued from this buffer two chunks ago has read it
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(sb + lane * 128 + ((j ^ sw) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (accum) tma_reduce_add_2d(&tmC, sb, col0, row0);
+            else tma_store_2d(&tmC, sb, col0, row0);
+            tma_store_commit();
           }
-          if (out_f32) {
-            float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+          sbuf ^= 1;
+        } else {
+          const int half = c & 1;  // two 32-column chunks share one 64-column (128-byte) staging row
+          if (half == 0) {
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+          }
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              if (col0 + i < p.N) {  // N % 4 == 0 is required
-                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                if (accum) {
-                  float4 old = *reinterpret_cast<const float4*>(dst + i);
-                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                }
-                *reinterpret_cast<float4*>(dst + i) = o;
-              }
+          for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            o.x = pack_bf16x2(v[8 * j], v[8 * j + 1]);
+            o.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+            o.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
+            o.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+            *reinterpret_cast<uint4*>(sb + lane * 128 + (((half * 4 + j) ^ sw) << 4)) = o;
+          }
+          const bool last_of_pair = half == 1 || col0 + 32 >= p.N || c == BN / 32 - 1;
+          if (last_of_pair) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmC, sb, col0 - half * 32, row0);
+              tma_store_commit();
             }
-          } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              if (col0 + i < p.N) {  // N % 8 == 0 is required
-                if (accum) {
-                  uint4 old = *reinterpret_cast<const uint4*>(dst + i);
-                  const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    float2 f = __bfloat1622float2(ob[j]);
-                    v[i + 2 * j] += f.x;
-                    v[i + 2 * j + 1] += f.y;
-                  }
-                }
-                uint4 o;
-                o.x = pack_bf16x2(v[i], v[i + 1]);
-                o.y = pack_bf16x2(v[i + 2], v[i + 3]);
-                o.z = pack_bf16x2(v[i + 4], v[i + 5]);
-                o.w = pack_bf16x2(v[i + 6], v[i + 7]);
-                *reinterpret_cast<uint4*>(dst + i) = o;
-              }
-            }
+            sbuf ^= 1;
           }
         }
       }
@@ -254,6 +265,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[buf]);
     }
+    if (lane == 0) tma_store_wait<0>();  // all of this warp's stores have landed before the CTA may exit
   }
 
   tc_fence_before_sync();
@@ -287,16 +299,16 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, row pitch `ld` elements.
-int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
-                      uint32_t box_inner, uint32_t box_outer) {
+// 2D tensor map (bf16 or fp32): `inner` contiguous elements per row, `outer` rows, row pitch `ld` elements.
+int make_tmap_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
+                 uint32_t box_outer, bool f32) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
   cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {ld * 2};
+  cuuint64_t strides[1] = {ld * (f32 ? 4 : 2)};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = fn(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -2000 - static_cast<int>(r);
@@ -307,13 +319,16 @@ static int g_num_sms = 0;
 template <int BN>
 static int launch_gemm(const void* A, const void* B, GemmArgs& p, long long lda, long long ldb, int max_ctas, cudaStream_t stream) {
   using S = GemmSmem<BN>;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmC;
   int rc;
-  if (!p.a_mn) rc = make_tmap_bf16_2d(&tmA, A, p.K, p.M, lda, GEMM_BK, GEMM_BM);
-  else rc = make_tmap_bf16_2d(&tmA, A, p.M, p.K, lda, 64, GEMM_BK);
+  if (!p.a_mn) rc = make_tmap_2d(&tmA, A, p.K, p.M, lda, GEMM_BK, GEMM_BM, false);
+  else rc = make_tmap_2d(&tmA, A, p.M, p.K, lda, 64, GEMM_BK, false);
   if (rc) return rc;
-  if (!p.b_mn) rc = make_tmap_bf16_2d(&tmB, B, p.K, p.N, ldb, GEMM_BK, BN);
-  else rc = make_tmap_bf16_2d(&tmB, B, p.N, p.K, ldb, 64, GEMM_BK);
+  if (!p.b_mn) rc = make_tmap_2d(&tmB, B, p.K, p.N, ldb, GEMM_BK, BN, false);
+  else rc = make_tmap_2d(&tmB, B, p.N, p.K, ldb, 64, GEMM_BK, false);
+  if (rc) return rc;
+  const bool f32 = p.flags & GEMM_OUT_F32;
+  rc = make_tmap_2d(&tmC, p.C, p.N, p.M, p.ldc, f32 ? 32 : 64, 32, f32);
   if (rc) return rc;
   p.tiles_m = (p.M + GEMM_BM - 1) / GEMM_BM;
   p.tiles_n = (p.N + BN - 1) / BN;
@@ -332,7 +347,7 @@ static int launch_gemm(const void* A, const void* B, GemmArgs& p, long long lda,
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   int tiles = p.tiles_m * p.tiles_n;
   if (tiles < ctas) ctas = tiles;
-  gemm_bf16_tcgen05_kernel<BN><<<ctas, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, p);
+  gemm_bf16_tcgen05_kernel<BN><<<ctas, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, tmC, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -348,6 +363,7 @@ extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void*
   using namespace b200;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (N % 8) || (ldc % 4) || (!(flags & GEMM_OUT_F32) && (ldc % 8))) return -10;
+  if ((flags & GEMM_ACCUMULATE) && !(flags & GEMM_OUT_F32)) return -12;  // accumulation is into fp32 only
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -11;
   GemmArgs p;
   p.C = C;

@@ -168,7 +168,8 @@ __global__ void gelu_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_
 constexpr int CE_THREADS = 512;
 __global__ void __launch_bounds__(CE_THREADS)
 cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels, float* __restrict__ loss,
-                     int V, long long ld, int ignore_index, float grad_scale, int write_grad) {
+                     int V, long long ld, int ignore_index, float grad_scale, const float* __restrict__ grad_scale_dev,
+                     int write_grad) {
   __shared__ float red_m[CE_THREADS / 32], red_s[CE_THREADS / 32];
   __shared__ float sh_max, sh_lse;
   const long long row = blockIdx.x;
@@ -210,7 +211,7 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __rest
   if (threadIdx.x == 0) loss[row] = ignored ? 0.f : lse - __bfloat162float(x[label]);
   if (!write_grad) return;
   __syncthreads();  // label logit read before it is overwritten
-  const float gs = ignored ? 0.f : grad_scale;
+  const float gs = ignored ? 0.f : grad_scale * (grad_scale_dev ? *grad_scale_dev : 1.f);
   for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
     float a[8], o[8];
     unpack8(reinterpret_cast<const uint4*>(x)[i], a);
@@ -370,12 +371,14 @@ extern "C" int b200_gelu_bwd(const void* x, const void* dy, void* dx, long long 
   return CHECK_LAUNCH();
 }
 // logits [rows, V] bf16 with row pitch ld; overwritten with the gradient when write_grad != 0.
+// The gradient is scaled by grad_scale * (*grad_scale_dev if given): e.g. 1 / (number of valid tokens) kept on the device.
 extern "C" int b200_cross_entropy(void* logits, const long long* labels, float* loss, long long rows, int V, long long ld,
-                                  int ignore_index, float grad_scale, int write_grad, cudaStream_t stream) {
+                                  int ignore_index, float grad_scale, const float* grad_scale_dev, int write_grad,
+                                  cudaStream_t stream) {
   if (V % 8 || ld % 8) return -10;
   if (rows <= 0) return 0;
   cross_entropy_kernel<<<static_cast<unsigned>(rows), CE_THREADS, 0, stream>>>(static_cast<__nv_bfloat16*>(logits), labels, loss, V, ld,
-                                                                             ignore_index, grad_scale, write_grad);
+                                                                             ignore_index, grad_scale, grad_scale_dev, write_grad);
   return CHECK_LAUNCH();
 }
 extern "C" int b200_embedding_fwd(const long long* ids, const void* table, void* out, long long tokens, int H, int vocab,

@@ -111,6 +111,12 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, const void
                ::"l"(tmap), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
                : "memory");
 }
+// C[tile] += smem tile (element-wise add performed by the memory system; fp32 here).
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* tmap, const void* smem_src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(tmap), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {

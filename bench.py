@@ -113,7 +113,7 @@ def run_ours(a):
     S = a.seq
     gbs = a.seqs_per_gpu * a.gpus
     g = torch.Generator().manual_seed(1234 + eng.tpl.dp_rank)
-    n_batches = 4
+    n_batches = a.warmup + a.steps  # a fresh synthetic batch every step
     host_ids = [torch.randint(0, cfg.vocab_size, (seqs_per_replica, S), generator=g).pin_memory() for _ in range(n_batches)]
     host_labels = [torch.cat([t[:, 1:], torch.full((seqs_per_replica, 1), -100, dtype=torch.long)], 1).pin_memory() for t in host_ids]
     loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
