@@ -93,6 +93,8 @@ class B200LlamaLayer(nn.Module):
             p.tp_sharded = True
         self._tables: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
         self.kv_cache = None  # set by the inference engine (paged or dense cache adaptor)
+        self.lora = nn.ModuleDict()  # target name -> LoRAAdapter (empty unless apply_lora was called)
+        self.lora_merged = False
 
     # ---- configuration by the engine -----------------------------------------
     def configure_tp(self, group, sequence_parallel: bool, sp_first: bool, sp_last: bool, backend: str = "nccl") -> None:
@@ -102,6 +104,66 @@ class B200LlamaLayer(nn.Module):
         self.tp_backend = backend
         for p in (self.input_norm_weight, self.post_norm_weight):
             p.sequence_parallel = self.sequence_parallel
+
+    # ---- LoRA ---------------------------------------------------------------------------
+    def _lora_dims(self):
+        D, H, I = self.head_dim, self.hidden, self.inter // self.tp_size
+        return {"q_proj": (H, self.hq * D), "k_proj": (H, self.hkv * D), "v_proj": (H, self.hkv * D),
+                "o_proj": (self.hq * D, H), "gate_proj": (H, I), "up_proj": (H, I), "down_proj": (I, H)}
+
+    def add_lora(self, cfg, tp_group=None, tp_size: int = 1) -> int:
+        from ..lora import COLWISE_TARGETS, LoRAAdapter, _tp_grad_hook
+        dims = self._lora_dims()
+        w = self.qkv_weight
+        n = 0
+        for t in cfg.target_modules:
+            if t not in dims or t in self.lora:
+                continue
+            fin, fout = dims[t]
+            ad = LoRAAdapter(fin, fout, cfg.r, cfg.alpha, cfg.dropout, w.dtype, w.device)
+            if tp_size > 1 and tp_group is not None:
+                rep = ad.lora_A.weight if t in COLWISE_TARGETS else ad.lora_B.weight  # the replicated half
+                dist_src = torch.distributed.get_global_rank(tp_group, 0)
+                torch.distributed.broadcast(rep.data, src=dist_src, group=tp_group)
+                rep.register_hook(_tp_grad_hook(tp_group, tp_size))
+                (ad.lora_B.weight if t in COLWISE_TARGETS else ad.lora_A.weight).tp_sharded = True
+            self.lora[t] = ad
+            n += 1
+        return n
+
+    def _lora_cat(self, x, names):
+        """Concatenated adapter outputs for the packed projection made of ``names`` (zeros where a target has no adapter)."""
+        if not self.lora or self.lora_merged:
+            return None
+        dims = self._lora_dims()
+        parts, any_ad = [], False
+        for t in names:
+            if t in self.lora:
+                parts.append(self.lora[t](x))
+                any_ad = True
+            else:
+                parts.append(x.new_zeros(*x.shape[:-1], dims[t][1]))
+        return torch.cat(parts, -1) if any_ad else None
+
+    def merge_lora(self) -> None:
+        if not self.lora or self.lora_merged:
+            return
+        D = self.head_dim
+        with torch.no_grad():
+            offs = {"q_proj": 0, "k_proj": self.hq * D, "v_proj": (self.hq + self.hkv) * D}
+            for t, o in offs.items():
+                if t in self.lora:
+                    dw = self.lora[t].delta_weight().to(self.qkv_weight.dtype)
+                    self.qkv_weight.data[o:o + dw.shape[0]] += dw
+            I = self.inter // self.tp_size
+            for t, o in {"gate_proj": 0, "up_proj": I}.items():
+                if t in self.lora:
+                    self.gate_up_weight.data[o:o + I] += self.lora[t].delta_weight().to(self.gate_up_weight.dtype)
+            if "o_proj" in self.lora:
+                self.o_weight.data += self.lora["o_proj"].delta_weight().to(self.o_weight.dtype)
+            if "down_proj" in self.lora:
+                self.down_weight.data += self.lora["down_proj"].delta_weight().to(self.down_weight.dtype)
+        self.lora_merged = True
 
     def _rope_tables(self, device) -> Tuple[torch.Tensor, torch.Tensor]:
         if self._tables is None or self._tables[0].device != device:
@@ -120,12 +182,19 @@ class B200LlamaLayer(nn.Module):
         residual = hidden_states
         x, _ = ops.rmsnorm(hidden_states, self.input_norm_weight, self.eps)
         # --- attention block
-        if sp:
+        use_lora = bool(self.lora) and not self.lora_merged
+        if sp and not use_lora:
             qkv = tp_comm.allgather_linear(x, self.qkv_weight, self.tp_group, self.tp_size, self.tp_backend)
         else:
-            if tp:
+            if sp:
+                x = tp_comm.gather_seq(x, self.tp_group, self.tp_size)
+            elif tp:
                 x = tp_comm.copy_to_tp(x, self.tp_group)
             qkv = ops.linear(x, self.qkv_weight)
+            if use_lora:
+                dl = self._lora_cat(x, ("q_proj", "k_proj", "v_proj"))
+                if dl is not None:
+                    qkv = qkv + dl
         qkv = qkv.reshape(B * S, (self.hq + 2 * self.hkv) * self.head_dim)
         if position_ids is None:
             pos = torch.arange(S, device=qkv.device, dtype=torch.int32).repeat(B)
@@ -139,26 +208,41 @@ class B200LlamaLayer(nn.Module):
             a = self.kv_cache.attend(self, qkv, B, S, pos)
         else:
             a = attn_ops.causal_attention_packed(qkv, B, S, self.hq, self.hkv, self.head_dim)
-        if sp:
-            o = tp_comm.linear_reducescatter(a.view(B, S, -1), self.o_weight, self.tp_group, self.tp_size, self.tp_backend)
+        a = a.view(B, S, -1)
+        if sp and not (use_lora and "o_proj" in self.lora):
+            o = tp_comm.linear_reducescatter(a, self.o_weight, self.tp_group, self.tp_size, self.tp_backend)
         else:
-            o = ops.linear(a.view(B, S, -1), self.o_weight)
-            if tp:
+            o = ops.linear(a, self.o_weight)
+            if use_lora and "o_proj" in self.lora:
+                o = o + self.lora["o_proj"](a)
+            if sp:
+                o = tp_comm.reduce_scatter_seq(o, self.tp_group, self.tp_size)
+            elif tp:
                 o = tp_comm.reduce_from_tp(o, self.tp_group)
         # --- MLP block (residual add fused into the norm)
         x, residual = ops.rmsnorm(o, self.post_norm_weight, self.eps, residual=residual)
-        if sp:
+        if sp and not use_lora:
             gu = tp_comm.allgather_linear(x, self.gate_up_weight, self.tp_group, self.tp_size, self.tp_backend)
         else:
-            if tp:
+            if sp:
+                x = tp_comm.gather_seq(x, self.tp_group, self.tp_size)
+            elif tp:
                 x = tp_comm.copy_to_tp(x, self.tp_group)
             gu = ops.linear(x, self.gate_up_weight)
+            if use_lora:
+                dl = self._lora_cat(x, ("gate_proj", "up_proj"))
+                if dl is not None:
+                    gu = gu + dl
         act = ops.swiglu(gu)
-        if sp:
+        if sp and not (use_lora and "down_proj" in self.lora):
             d = tp_comm.linear_reducescatter(act, self.down_weight, self.tp_group, self.tp_size, self.tp_backend)
         else:
             d = ops.linear(act, self.down_weight)
-            if tp:
+            if use_lora and "down_proj" in self.lora:
+                d = d + self.lora["down_proj"](act)
+            if sp:
+                d = tp_comm.reduce_scatter_seq(d, self.tp_group, self.tp_size)
+            elif tp:
                 d = tp_comm.reduce_from_tp(d, self.tp_group)
         out = residual + d
         if sp and self.sp_last:

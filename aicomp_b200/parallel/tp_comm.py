@@ -142,6 +142,14 @@ class _GatherFromSP(torch.autograd.Function):
         return g[:, ctx.rank * S_loc:(ctx.rank + 1) * S_loc].contiguous(), None, None, None
 
 
+def gather_seq(x, group, size):
+    return _GatherSeq.apply(x, group, size)
+
+
+def reduce_scatter_seq(x, group, size):
+    return _ReduceScatterSeq.apply(x, group, size)
+
+
 def scatter_to_sp(x, group, rank, size):
     if x.shape[1] % size:
         raise ValueError(f"sequence length {x.shape[1]} is not divisible by tp_size {size}")
