@@ -65,7 +65,7 @@ class Optimus_p:
                  # extensions of this framework
                  dtype: Optional[torch.dtype] = None, fused_kernels: Optional[bool] = None, sequence_parallel: bool = True,
                  dp_backend: str = "fused", tp_backend: str = "fused", example_inputs: Optional[Dict[str, Any]] = None,
-                 input_names: Optional[List[str]] = None, loss_fn=None, init_fn=None):
+                 input_names: Optional[List[str]] = None, loss_fn=None, init_fn=None, trace_kwargs: Optional[Dict[str, Any]] = None):
         self.comm = Comm(use_gpu=use_gpu)
         self.use_gpu = self.comm.use_gpu
         self.device = self.comm.device
@@ -122,10 +122,10 @@ class Optimus_p:
         if ir_analyze == IR_Anal.SEQUENTIAL and world > 1:
             for turn in range(self.comm.local_world_size):
                 if turn == self.comm.local_rank:
-                    self.ir.retrieve_IR(dynamo_capture=dynamo_capture, example_inputs=example_inputs, input_names=input_names)
+                    self.ir.retrieve_IR(dynamo_capture=dynamo_capture, example_inputs=example_inputs, input_names=input_names, const_kwargs=trace_kwargs)
                 self.comm.barrier()
         else:
-            self.ir.retrieve_IR(dynamo_capture=dynamo_capture, example_inputs=example_inputs, input_names=input_names)
+            self.ir.retrieve_IR(dynamo_capture=dynamo_capture, example_inputs=example_inputs, input_names=input_names, const_kwargs=trace_kwargs)
         self.model_type = self.ir.model_type
         table = None
         if ir_analyze != IR_Anal.SINGLE or self.comm.rank == 0:

@@ -36,7 +36,8 @@ class IR:
 
     # ---- capture ------------------------------------------------------------
     def retrieve_IR(self, dynamo_capture: bool = False, example_inputs: Optional[Dict[str, Any]] = None,
-                    input_names: Optional[List[str]] = None, use_kv_cache: bool = False, for_training: bool = True) -> fx.GraphModule:
+                    input_names: Optional[List[str]] = None, use_kv_cache: bool = False, for_training: bool = True,
+                    const_kwargs: Optional[Dict[str, Any]] = None) -> fx.GraphModule:
         e = self.engine
         fused = bool(getattr(e, "fused_kernels", False))
         leaf_classes: Tuple[str, ...] = ()
@@ -49,7 +50,8 @@ class IR:
             from .export_capture import export_to_module_graph
             res = export_to_module_graph(self.module, input_names=input_names, example_inputs=example_inputs, leaf_classes=leaf_classes)
         else:
-            res = trace_model(self.module, input_names=input_names, example_inputs=example_inputs, leaf_classes=leaf_classes)
+            res = trace_model(self.module, input_names=input_names, example_inputs=example_inputs, leaf_classes=leaf_classes,
+                              const_kwargs=const_kwargs)
         self.gm, self.input_names, self.model_type = res.gm, res.input_names, res.model_type
         if fused:
             from .rewrite import substitute_kernels
