@@ -65,7 +65,7 @@ def _rows(t: torch.Tensor) -> torch.Tensor:
 # ---------------------------------------------------------------------- GEMM
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: Optional[torch.Tensor] = None,
          out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False, bias: Optional[torch.Tensor] = None,
-         alpha: float = 1.0, bn: int = 0, max_ctas: int = 0) -> torch.Tensor:
+         alpha: float = 1.0, bn: int = 0, max_ctas: int = 0, ksplit: int = 1) -> torch.Tensor:
     """``C[M,N] (+)= alpha * A @ B^T (+ bias)`` on tcgen05 tensor cores.
 
     ``a`` is ``[M,K]`` (or ``[K,M]`` when ``a_mn``), ``b`` is ``[N,K]`` (or
@@ -106,7 +106,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     lib = _lib.require()
     rc = lib.b200_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(bias), M, N, K,
                             a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn), flags, float(alpha),
-                            bn, max_ctas, _lib.err_word(a.device).data_ptr(), _lib.stream_ptr())
+                            bn, max_ctas, ksplit, _lib.err_word(a.device).data_ptr(), _lib.stream_ptr())
     _lib.check_rc(rc, "gemm")
     _count()
     return out
@@ -152,9 +152,28 @@ class _LinearFn(torch.autograd.Function):
         return dx, dw, db
 
 
+def _linear_small_m(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """Decode-sized GEMM (few rows): weight streaming is the bound, so K is split over enough CTAs to pull on all of
+    HBM; partial products meet in an fp32 buffer through the reduce-add epilogue and are cast once."""
+    x2 = _rows(x)
+    M, K = x2.shape
+    N = w.shape[0]
+    tiles = ((M + 127) // 128) * ((N + 127) // 128)
+    ks = max(1, min(16, (2 * 148) // max(tiles, 1), K // 512))
+    if ks == 1:
+        y = torch.empty(*x.shape[:-1], N, dtype=x.dtype, device=x.device)
+        gemm(x2, w, bias=bias, out=y.view(-1, N), bn=128)
+        return y
+    acc = torch.zeros(M, N, dtype=torch.float32, device=x.device)
+    gemm(x2, w, bias=bias, out=acc, accumulate=True, bn=128, ksplit=ks)
+    return acc.to(x.dtype).view(*x.shape[:-1], N)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     if not kernels_for(x, w):
         return F.linear(x, w, bias)
+    if not torch.is_grad_enabled() and x.numel() // x.shape[-1] <= 256:
+        return _linear_small_m(x, w, bias)
     return _LinearFn.apply(x, w, bias)
 
 

@@ -47,7 +47,7 @@ def _split_packed(qkv: torch.Tensor, B: int, S: int, hq: int, hkv: int, D: int):
 def causal_attention_packed(qkv: torch.Tensor, B: int, S: int, hq: int, hkv: int, D: int, scale: Optional[float] = None
                             ) -> torch.Tensor:
     from . import flash
-    if flash.supported(qkv, D):
+    if qkv.is_cuda and flash.supported(qkv, D):
         return flash.flash_attention_packed(qkv, B, S, hq, hkv, D, scale)
     q, k, v = _split_packed(qkv, B, S, hq, hkv, D)
     if qkv.is_cuda:

@@ -39,6 +39,7 @@ struct GemmArgs {
   int flags;
   float alpha;
   int tiles_m, tiles_n;
+  int ksplit;  // >1: each output tile is computed by `ksplit` work items over disjoint K ranges (fp32 reduce-add epilogue)
   int* err;
 };
 
@@ -82,8 +83,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.tiles_m * p.tiles_n;
-  const int nkb = (p.K + GEMM_BK - 1) / GEMM_BK;
+  const int mn_tiles = p.tiles_m * p.tiles_n;
+  const int num_tiles = mn_tiles * p.ksplit;
+  const int nkb_total = (p.K + GEMM_BK - 1) / GEMM_BK;
+  const int nkb_per = (nkb_total + p.ksplit - 1) / p.ksplit;
 
   if (threadIdx.x == 0) {
     cta_abort = 0;
@@ -117,9 +120,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int tm, tn;
-        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        tile_coords(tile % mn_tiles, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * GEMM_BM, n0 = tn * BN;
-        for (int kb = 0; kb < nkb; ++kb) {
+        const int kb_lo = (tile / mn_tiles) * nkb_per;
+        const int kb_hi = min(nkb_total, kb_lo + nkb_per);
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, p.err, ERR_WAIT_EMPTY, &cta_abort)) { ok = false; break; }
           uint8_t* sA = smem + s * S::STAGE_BYTES;
           uint8_t* sB = sA + S::A_BYTES;
@@ -161,7 +166,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         if (!mbar_wait(&tmem_empty[buf], ((it >> 1) & 1) ^ 1, p.err, ERR_WAIT_TMEM_EMPTY, &cta_abort)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < nkb; ++kb) {
+        const int kb_lo = (tile / mn_tiles) * nkb_per;
+        const int kb_hi = min(nkb_total, kb_lo + nkb_per);
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&full_bar[s], ph, p.err, ERR_WAIT_FULL, &cta_abort)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t a_base = smem_u32(smem + s * S::STAGE_BYTES);
@@ -172,7 +179,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                                           : make_smem_desc_sw128(a_base + k * 32, 16, 1024);
             const uint64_t bdesc = p.b_mn ? make_smem_desc_sw128(b_base + k * 2048, 8192, 1024)
                                           : make_smem_desc_sw128(b_base + k * 32, 16, 1024);
-            umma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
+            umma_bf16_ss(d_tmem, adesc, bdesc, idesc, ((kb - kb_lo) | k) != 0);
           }
           umma_commit(&empty_bar[s]);
           if (++s == S::STAGES) { s = 0; ph ^= 1; }
@@ -195,7 +202,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
       int tm, tn;
-      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      tile_coords(tile % mn_tiles, p.tiles_m, p.tiles_n, tm, tn);
+      const bool first_split = tile < mn_tiles;  // bias is added by exactly one of the K splits
       const int buf = it & 1;
       ok = mbar_wait(&tmem_full[buf], (it >> 1) & 1, p.err, ERR_WAIT_TMEM_FULL, &cta_abort);
       ok = __all_sync(0xffffffffu, ok);
@@ -214,7 +222,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         float v[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-        if (has_bias) {
+        if (has_bias && first_split) {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             if (col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
@@ -345,7 +353,7 @@ static int launch_gemm(const void* A, const void* B, GemmArgs& p, long long lda,
   }
   int ctas = g_num_sms;
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
-  int tiles = p.tiles_m * p.tiles_n;
+  int tiles = p.tiles_m * p.tiles_n * p.ksplit;
   if (tiles < ctas) ctas = tiles;
   gemm_bf16_tcgen05_kernel<BN><<<ctas, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, tmC, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
@@ -359,7 +367,7 @@ static int launch_gemm(const void* A, const void* B, GemmArgs& p, long long lda,
 // bn: 0 = pick, else 128 or 256.  max_ctas limits the persistent grid (0 = all SMs).
 extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
                               long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int flags, float alpha,
-                              int bn, int max_ctas, int* err, cudaStream_t stream) {
+                              int bn, int max_ctas, int ksplit, int* err, cudaStream_t stream) {
   using namespace b200;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (N % 8) || (ldc % 4) || (!(flags & GEMM_OUT_F32) && (ldc % 8))) return -10;
@@ -374,6 +382,16 @@ extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, const void*
   p.flags = flags;
   p.alpha = alpha;
   p.err = err;
+  // split-K: partial products are summed by the fp32 reduce-add epilogue, so C must be fp32 and pre-initialised
+  const int nkb_total = (K + GEMM_BK - 1) / GEMM_BK;
+  if (ksplit < 1) ksplit = 1;
+  if (ksplit > nkb_total) ksplit = nkb_total;
+  if (ksplit > 1) {
+    if ((flags & (GEMM_OUT_F32 | GEMM_ACCUMULATE)) != (GEMM_OUT_F32 | GEMM_ACCUMULATE)) return -13;
+    const int per = (nkb_total + ksplit - 1) / ksplit;
+    ksplit = (nkb_total + per - 1) / per;  // no empty split
+  }
+  p.ksplit = ksplit;
   if (bn == 0) {
     // 256-wide tiles halve A re-reads; fall back to 128 when that fills the SMs better.
     long long t256 = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256);

@@ -145,6 +145,30 @@ class ServingEngine:
         self.decode_steps += 1
         return g["out"][:n].tolist()
 
+    def warmup(self, max_batch: Optional[int] = None, prompt_len: int = 256) -> None:
+        """Run one prefill and capture the decode graphs for every batch bucket up to ``max_batch`` (untimed set-up)."""
+        max_batch = max_batch or self.max_seqs
+        reqs = []
+        for i in range(min(max_batch, self.max_seqs)):
+            r = Request(rid=-1 - i, prompt=[1] * (prompt_len if i == 0 else 4), max_new_tokens=4)
+            if not self.cache.can_admit(r.prompt_len + 8):
+                break
+            r.slot = self.cache.add_sequence(r.prompt_len + 8)
+            r.generated = [self.prefill(r)] if i == 0 else [1]
+            self.cache.seq_len[r.slot] = r.prompt_len
+            reqs.append(r)
+        for b in _BUCKETS:
+            if b > len(reqs):
+                break
+            for _ in range(3 if self.use_graphs else 1):  # two eager runs, then the capture
+                self.decode(reqs[:b])
+        for r in reqs:
+            self.cache.free_sequence(r.slot)
+        self.decode_steps = 0
+        self.prefill_tokens = 0
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+
     # ---- request loop ------------------------------------------------------------------------------------
     def serve(self, requests: List[Request], realtime: bool = True, max_wall_s: Optional[float] = None) -> Dict[str, float]:
         """Run ``requests`` to completion.  With ``realtime`` arrivals follow the wall clock; otherwise the clock

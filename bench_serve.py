@@ -40,6 +40,7 @@ def main():
         model = LlamaForCausalLM(cfg)
     eng = ServingEngine(model, tp_size=a.tp, max_seqs=a.max_seqs, max_seq_len=2048 + 512 + 16, cuda_graphs=not a.no_graphs)
     reqs = make_requests(a.requests, a.rate, seed=0)
+    eng.warmup()
     ops.reset_launch_count()
     m = eng.serve(reqs, realtime=not a.fast_clock)
     ops.check_errors()

@@ -79,3 +79,19 @@ def test_wgrad_accumulates_into_main_grad():
     ref = 2 * (torch.ones(256, 384, device="cuda").t() @ x.float())
     assert torch.allclose(w.main_grad, ref, rtol=1e-3, atol=1e-2)
     ops.check_errors()
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 4096, 4096), (64, 6144, 4096), (100, 4096, 14336), (256, 1024, 512)])
+def test_small_m_linear_split_k(M, N, K):
+    torch.manual_seed(4)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
+    b = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        y = ops.linear(x, w, b)
+    ref = x.float() @ w.float().t() + b.float()
+    assert (y.float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-2
+    acc = torch.zeros(M, N, device="cuda")
+    ops.gemm(x, w, out=acc, accumulate=True, ksplit=7, bn=128)
+    assert torch.allclose(acc, x.float() @ w.float().t(), rtol=1e-3, atol=2e-2)
+    ops.check_errors()
