@@ -276,8 +276,20 @@ def layernorm(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: 
 
 
 # ---------------------------------------------------------------------- RoPE
+_rope_cache = {}
+
+
 def rope_tables(max_pos: int, dim: int, theta: float, device, scaling: Optional[dict] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """fp32 cos/sin tables ``[max_pos, dim/2]`` (HF default rope; optional llama3 frequency scaling)."""
+    """fp32 cos/sin tables ``[max_pos, dim/2]`` (HF default rope; optional llama3 frequency scaling); shared by all layers."""
+    key = (max_pos, dim, float(theta), str(device), repr(sorted(scaling.items())) if scaling else None)
+    hit = _rope_cache.get(key)
+    if hit is None:
+        hit = _rope_tables(max_pos, dim, theta, device, scaling)
+        _rope_cache[key] = hit
+    return hit
+
+
+def _rope_tables(max_pos: int, dim: int, theta: float, device, scaling: Optional[dict] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     inv_freq = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32, device=device) / dim))
     if scaling and scaling.get("rope_type", scaling.get("type")) == "llama3":
         factor = scaling["factor"]

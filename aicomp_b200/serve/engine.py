@@ -54,7 +54,7 @@ class ServingEngine:
                 num_pages = 512
         first = min(l.layer_idx for l in self.layers)
         self.cache = PagedKVCache(len(self.layers), l0.hkv, l0.head_dim, num_pages, max_seqs, self.max_blocks, dtype, self.device,
-                                  pool=pool, layer_offset=first)
+                                  pool=pool, layer_offset=first, q_heads=l0.hq)
         self.adaptor = PagedKVAdaptor(self.cache)
         for l in self.layers:
             l.kv_cache = self.adaptor

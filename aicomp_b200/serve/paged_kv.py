@@ -50,7 +50,8 @@ class PagedKVCache:
     """Per-stage paged cache for ``n_layers`` layers; pools are views ``[layers, 2, pages, 16, kv_heads, D]``."""
 
     def __init__(self, n_layers: int, kv_heads: int, head_dim: int, num_pages: int, max_seqs: int, max_blocks_per_seq: int,
-                 dtype=torch.bfloat16, device=None, pool: Optional[torch.Tensor] = None, layer_offset: int = 0):
+                 dtype=torch.bfloat16, device=None, pool: Optional[torch.Tensor] = None, layer_offset: int = 0,
+                 q_heads: Optional[int] = None):
         self.n_layers, self.kv_heads, self.head_dim = n_layers, kv_heads, head_dim
         self.num_pages, self.max_seqs, self.max_blocks = num_pages, max_seqs, max_blocks_per_seq
         self.dtype, self.device = dtype, device
@@ -67,7 +68,16 @@ class PagedKVCache:
         self.seq_pages: Dict[int, List[int]] = {}
         self.seq_len: Dict[int, int] = {}
         self.free_slots: List[int] = list(range(max_seqs - 1, -1, -1))
+        # Split-KV partials of the decode kernel.  Sized once for the worst batch: CUDA graphs record its address, so it
+        # must never be reallocated afterwards.
         self._scratch: Optional[torch.Tensor] = None
+        self.q_heads = q_heads or kv_heads * 8
+        if device is not None and torch.device(device).type == "cuda":
+            worst = max(n * self._splits_for(n) for n in range(1, max_seqs + 1) if self._splits_for(n) > 1) if max_seqs else 0
+            self._scratch = torch.empty(max(1, worst) * self.q_heads * (head_dim + 2), dtype=torch.float32, device=device)
+
+    def _splits_for(self, n: int) -> int:
+        return max(1, min(16, (2 * 148 + n * self.kv_heads - 1) // (n * self.kv_heads)))
 
     # ---- sequence management (host side) -----------------------------------------------------
     def pages_needed(self, tokens: int) -> int:
@@ -146,12 +156,12 @@ class PagedKVCache:
             lib = _lib.require()
             out = torch.empty(n, hq * D, dtype=q.dtype, device=q.device)
             max_len_pages = table.shape[1]
-            splits = max(1, min(16, (2 * 148 + n * self.kv_heads - 1) // (n * self.kv_heads)))
+            splits = self._splits_for(n) if n <= self.max_seqs else 1
             scratch = None
             need = lib.b200_paged_decode_scratch_floats(n, hq, splits)
             if need:
                 if self._scratch is None or self._scratch.numel() < need:
-                    self._scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+                    raise RuntimeError("decode scratch too small: construct PagedKVCache with the model's q_heads")
                 scratch = self._scratch
             rc = lib.b200_paged_decode(q.data_ptr(), q.stride(0), k_pool.data_ptr(), v_pool.data_ptr(), table.data_ptr(),
                                        max_len_pages, seq_lens.data_ptr(), n, hq, self.kv_heads, D, float(scale), splits,

@@ -12,7 +12,7 @@ def test_paged_decode_matches_reference(hq, hkv, n, maxlen):
     torch.manual_seed(0)
     D = 128
     blocks = (maxlen + PAGE - 1) // PAGE
-    cache = PagedKVCache(1, hkv, D, num_pages=n * blocks + 1, max_seqs=n, max_blocks_per_seq=blocks, device="cuda")
+    cache = PagedKVCache(1, hkv, D, num_pages=n * blocks + 1, max_seqs=n, max_blocks_per_seq=blocks, device="cuda", q_heads=hq)
     lens = torch.randint(1, maxlen + 1, (n,))
     lens[0] = maxlen
     slots = [cache.add_sequence(int(l)) for l in lens]
