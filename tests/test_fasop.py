@@ -1,0 +1,88 @@
+"""FASOP: partition solvers agree, the simulator obeys schedule invariants, the search ranks sensibly."""
+import numpy as np
+import pytest
+from hypothesis import given, settings, strategies as st
+
+from aicomp_b200.fasop.config import MODEL_CONFIGS, NODE_TYPES
+from aicomp_b200.fasop.partitioners import partition, stage_costs
+from aicomp_b200.fasop.profiledb import ProfileDB
+from aicomp_b200.fasop.search import FasopConfig, enumerate_parallel_strategies, run_strategy_search
+from aicomp_b200.fasop.sim1f1b import simulate, stage_order
+
+
+def _llama70b_10layer_costs():
+    """The reference's solver benchmark case: A40 profile of llama70b, reduced to 10 layers (82 nodes), TP2, MBS4."""
+    import os
+    path = "/root/reference/fasop/known_cost/llama70b_A40_2.npz"
+    if os.path.exists(path):
+        row = np.load(path)["data"][2]
+    else:  # the published row (BASELINE table 2.3, tp 2 / mbs 4)
+        row = np.array([1.154, 3.619, 0.470, 0.571, 2.249, 7.135, 0.094, 5.451, 5.944, 53.149])
+    seq = [0] + list(range(1, 9)) * 10 + [9]
+    return np.array([row[i] for i in seq]) * 3.0
+
+
+def test_solvers_agree_on_reference_case():
+    cost = _llama70b_10layer_costs()
+    sizes = {m: partition(m, cost, 4, layer_level=False, num_mb=8) for m in ("minmax", "dp", "ilp", "bruteforce")}
+    best = max(stage_costs(cost, sizes["bruteforce"]))
+    for m, s in sizes.items():
+        assert sum(s) == 82 and len(s) == 4
+        assert max(stage_costs(cost, s)) <= best * (1.0 + (0.05 if m == "minmax" else 1e-9)), (m, s)
+    assert sizes["dp"] == sizes["bruteforce"] == [25, 24, 24, 9]
+
+
+def test_layer_level_cuts_respected():
+    cost = _llama70b_10layer_costs()
+    for m in ("minmax", "dp", "ilp", "bruteforce", "optimus-even"):
+        s = partition(m, cost, 4, layer_level=True, num_mb=8)
+        c = 0
+        for n in s[:-1]:
+            c += n
+            assert (c - 1) % 8 == 0, (m, s)
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.integers(1, 5), st.integers(1, 9), st.lists(st.floats(0.1, 5.0), min_size=5, max_size=5),
+       st.lists(st.floats(0.1, 9.0), min_size=5, max_size=5), st.floats(0.0, 1.0))
+def test_simulator_invariants(P, M, f, b, send):
+    f, b = f[:P], b[:P]
+    ends, tl = simulate(f, b, [send] * (P - 1), [send] * (P - 1), M)
+    for s in range(P):
+        assert [(k, m) for k, m, _, _ in tl[s]] == stage_order(s, P, M)
+        for (k0, m0, s0, e0), (k1, m1, s1, e1) in zip(tl[s], tl[s][1:]):
+            assert s1 >= e0 - 1e-12            # a stage does one thing at a time
+    # lower bounds: the busiest stage's work, and the critical path of the first micro-batch
+    assert max(ends) >= max(M * (x + y) for x, y in zip(f, b)) - 1e-9
+    assert max(ends) >= sum(f) + sum(b) + 2 * (P - 1) * send - 1e-9
+    if P == 1:
+        assert abs(ends[0] - M * (f[0] + b[0])) < 1e-9
+
+
+def test_enumeration_covers_world():
+    for tp, dp, pp, mbs in enumerate_parallel_strategies(8, 128, 28):
+        assert tp * dp * pp == 8 and 128 % (dp * mbs) == 0
+
+
+def test_search_llama3b_on_8_b200():
+    cfg = FasopConfig([("B200", 8)], "llama3b", gbs=[128])
+    res = run_strategy_search(cfg)
+    assert len(res) > 20
+    assert all(r.step_time > 0 for r in res)
+    ok = [r for r in res if not r.is_oom]
+    assert ok and ok[0].rank == 1 and ok == sorted(ok, key=lambda r: r.total_time)
+    # a 3B model fits one B200: pure data parallelism must be feasible
+    assert any(r.tp == 1 and r.pp == 1 and r.dp == 8 for r in ok)
+
+
+def test_profiledb_reads_reference_format(tmp_path):
+    from aicomp_b200.fasop.profiledb import save_profile
+    m = MODEL_CONFIGS["llama3b"]
+    fwd = np.arange(40, dtype=float).reshape(4, 10) + 1
+    save_profile(str(tmp_path / "llama3b_B200_1.npz"), fwd)
+    db = ProfileDB(m, "B200", str(tmp_path))
+    f, b = db.node_times(1, 2)
+    assert np.allclose(f, fwd[1] * 1e-3) and np.allclose(b, 2 * fwd[1] * 1e-3)   # forward+backward = 3x forward
+    save_profile(str(tmp_path / "llama3b_B200_2.npz"), fwd, fwd * 1.7)
+    f, b = ProfileDB(m, "B200", str(tmp_path)).node_times(2, 1)
+    assert np.allclose(b, 1.7 * fwd[0] * 1e-3)
