@@ -248,3 +248,42 @@ extern "C" int b200_kv_push(const void* src_pool, void* dst_pool, const int* src
                                              static_cast<unsigned int*>(done_counter));
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+// ---------------------------------------------------------------- reduce staged partial results
+// out[i] = sum_p in[p * part_stride + i]  (bf16 in, fp32 add, bf16 out): the local half of GEMM -> reduce-scatter,
+// after every tensor-parallel peer's GEMM epilogue has stored its partial tile rows into this rank's staging buffer.
+namespace b200 {
+__global__ void __launch_bounds__(256)
+sum_parts_bf16_kernel(const uint4* __restrict__ in, int parts, long long part_stride16, uint4* __restrict__ out, long long n16) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n16;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int p = 0; p < parts; ++p) {
+      const uint4 u = in[p * part_stride16 + i];
+      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(b[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    out[i] = o;
+  }
+}
+}  // namespace b200
+
+extern "C" int b200_sum_parts_bf16(const void* in, int parts, long long part_stride_elems, void* out, long long n, cudaStream_t stream) {
+  if (n % 8 || part_stride_elems % 8) return -10;
+  if (n <= 0) return 0;
+  long long n16 = n / 8;
+  long long blocks = (n16 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  b200::sum_parts_bf16_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(static_cast<const uint4*>(in), parts, part_stride_elems / 8,
+                                                                          static_cast<uint4*>(out), n16);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

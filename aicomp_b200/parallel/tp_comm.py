@@ -164,7 +164,7 @@ def allgather_linear(x: torch.Tensor, w: torch.Tensor, group, size: int, backend
     """``all_gather_seq(x) @ w^T`` for a column-parallel weight shard ``w [N/tp, K]``."""
     if backend == "fused":
         from . import fused_tp
-        if fused_tp.usable(x, w, group):
+        if fused_tp.usable_ag(x, w, group):
             return fused_tp.allgather_gemm(x, w, group, size)
     return ops.linear(_GatherSeq.apply(x, group, size), w)
 
@@ -173,6 +173,6 @@ def linear_reducescatter(x: torch.Tensor, w: torch.Tensor, group, size: int, bac
     """``reduce_scatter_seq(x @ w^T)`` for a row-parallel weight shard ``w [N, K/tp]``."""
     if backend == "fused":
         from . import fused_tp
-        if fused_tp.usable(x, w, group):
+        if fused_tp.usable_rs(x, w, group):
             return fused_tp.gemm_reducescatter(x, w, group, size)
     return _ReduceScatterSeq.apply(ops.linear(x, w), group, size)

@@ -15,12 +15,19 @@ def build_model(name: str):
         cfg = LlamaConfig(num_hidden_layers=4, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, intermediate_size=128,
                           vocab_size=512, max_position_embeddings=128, tie_word_embeddings=False)
         return LlamaForCausalLM(cfg)
+    if name == "llama_d128":  # head_dim 128 and tile-sized widths: exercises the sm_100a attention / fused TP kernels
+        from transformers import LlamaConfig, LlamaForCausalLM
+        cfg = LlamaConfig(num_hidden_layers=2, hidden_size=512, num_attention_heads=4, num_key_value_heads=2, intermediate_size=1024,
+                          vocab_size=512, max_position_embeddings=512, tie_word_embeddings=False)
+        return LlamaForCausalLM(cfg)
     if name == "mlp":
         return nn.Sequential(*[m for _ in range(6) for m in (nn.Linear(32, 32), nn.ReLU())])
     raise ValueError(name)
 
 
 def make_batch(name: str, batch: int, seed: int = 0, seq: int = 16):
+    if name == "llama_d128" and seq == 16:
+        seq = 256
     g = torch.Generator().manual_seed(1000 + seed)
     if name == "mlp":
         x = torch.randn(batch, 32, generator=g)

@@ -31,3 +31,22 @@ def test_pp2_dp2_training_matches_across_backends():
     lb = [r["losses"] for r in b if r["losses"][0] is not None][0]
     for x, y in zip(la, lb):
         assert abs(x - y) < 2e-2 * abs(x)
+
+
+def test_fused_tp_kernels_2gpu():
+    _need(2)
+    res = run_workers("gpu_collectives_worker", 2, {"tests": ["tp_fused"], "T": 2048}, timeout=300, env_extra={"NCCL_NVLS_ENABLE": "0"})
+    for r in res:
+        for k, v in r["tp_fused"].items():
+            if k.endswith("_err"):
+                assert v < 2e-2, (k, v)
+    print({k: round(v, 4) for k, v in res[0]["tp_fused"].items()})
+
+
+def test_tp2_training_fused_matches_nccl_backend():
+    _need(2)
+    base = {"model": "llama_d128", "tp": 2, "pp": 1, "num_mb": 1, "steps": 3, "batch": 1, "use_gpu": True, "dtype": "bfloat16", "seq": 256}
+    a = run_workers("train_worker", 2, dict(base, tp_backend="nccl"), timeout=300, env_extra={"NCCL_NVLS_ENABLE": "0"})
+    b = run_workers("train_worker", 2, dict(base, tp_backend="fused"), timeout=300, env_extra={"NCCL_NVLS_ENABLE": "0"})
+    for x, y in zip(a[0]["losses"], b[0]["losses"]):
+        assert abs(x - y) < 3e-2 * abs(x), (a[0]["losses"], b[0]["losses"])

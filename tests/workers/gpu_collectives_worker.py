@@ -89,6 +89,53 @@ def main():
         out["kv_push"] = {"ok": bool(ok)}
         ops.check_errors()
 
+    if "tp_fused" in a["tests"]:
+        from aicomp_b200.parallel import fused_tp
+        T, H, Nq, I = a.get("T", 4096), 4096, 6144 // world, 14336 // world
+        Tl = T // world
+        res = {}
+
+        def timed(fn, iters=8):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize(); dist.barrier()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(iters):
+                fn()
+            e.record(); torch.cuda.synchronize()
+            t = torch.tensor([s.elapsed_time(e) / iters], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return t.item()
+
+        # all-gather -> GEMM (QKV-like and gate/up-like)
+        for name, N, K in (("qkv", Nq, H), ("gate_up", 2 * I, H)):
+            x_local = torch.randn(Tl, K, device=dev, dtype=torch.bfloat16)
+            w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
+            y = fused_tp._ag_gemm_raw(x_local, w, group)
+            xg = torch.empty(T, K, device=dev, dtype=torch.bfloat16)
+            dist.all_gather_into_tensor(xg, x_local)
+            ref = xg.float() @ w.float().t()
+            res[f"ag_{name}_err"] = ((y.float() - ref).abs().max() / ref.abs().max()).item()
+            res[f"ag_{name}_fused_ms"] = timed(lambda: fused_tp._ag_gemm_raw(x_local, w, group))
+            res[f"ag_{name}_nccl_ms"] = timed(lambda: (dist.all_gather_into_tensor(xg, x_local), ops.gemm(xg, w)))
+            res[f"ag_{name}_gemm_only_ms"] = timed(lambda: ops.gemm(xg, w))
+        # GEMM -> reduce-scatter (out-proj-like and down-proj-like)
+        for name, N, K in (("o_proj", H, 4096 // world), ("down", H, I)):
+            x = torch.randn(T, K, device=dev, dtype=torch.bfloat16)
+            w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
+            y = fused_tp._gemm_rs_raw(x, w, group)
+            full = (x.float() @ w.float().t())
+            dist.all_reduce(full)
+            ref = full[comm.rank * Tl:(comm.rank + 1) * Tl]
+            res[f"rs_{name}_err"] = ((y.float() - ref).abs().max() / ref.abs().max()).item()
+            rs_out = torch.empty(Tl, N, device=dev, dtype=torch.bfloat16)
+            res[f"rs_{name}_fused_ms"] = timed(lambda: fused_tp._gemm_rs_raw(x, w, group))
+            res[f"rs_{name}_nccl_ms"] = timed(lambda: dist.reduce_scatter_tensor(rs_out, ops.gemm(x, w)))
+            res[f"rs_{name}_gemm_only_ms"] = timed(lambda: ops.gemm(x, w))
+        ops.check_errors()
+        out["tp_fused"] = res
+
     worker_report(out)
     comm.barrier()
 
