@@ -67,3 +67,25 @@ def test_single_mode_broadcasts_assignment():
     ref, cs = reference_losses("gpt2", steps=2, batch=4, num_mb=2)
     res = run_workers("train_worker", 2, {"model": "gpt2", "pp": 2, "num_mb": 2, "steps": 2, "batch": 4, "ir": "SINGLE"})
     _check(res, ref, cs)
+
+
+@pytest.mark.parametrize("model", ["gpt2", "llama"])
+def test_export_capture_matches_tracer(model):
+    """dynamo_capture=True (torch.export path) yields a graph that computes the same logits, with dynamic shapes."""
+    import torch
+    from aicomp_b200.graph.export_capture import export_to_module_graph
+    from tests.models_small import build_model, make_batch
+    m = build_model(model).eval()
+    tr = export_to_module_graph(m)
+    ids, _ = make_batch(model, 3, seq=11)
+    with torch.no_grad():
+        ref = m(input_ids=ids, use_cache=False).logits
+        out = tr.gm(ids)["logits"]
+    assert torch.allclose(out, ref, atol=1e-5)
+    assert sum(1 for n in tr.gm.graph.nodes if n.op == "call_module") >= 4
+
+
+def test_pp2_with_export_capture():
+    ref, cs = reference_losses("gpt2", steps=2, batch=4, num_mb=2)
+    res = run_workers("train_worker", 2, {"model": "gpt2", "pp": 2, "num_mb": 2, "steps": 2, "batch": 4, "dynamo": True})
+    _check(res, ref, cs)

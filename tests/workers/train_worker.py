@@ -20,12 +20,13 @@ def main():
                   tp_size=a.get("tp", 1), activation_ckpt=a.get("act_ckpt", False), partitioner=a.get("partitioner", "auto"),
                   dtype=getattr(torch, a["dtype"]) if a.get("dtype") else None, sequence_parallel=a.get("sp", True),
                   dp_backend=a.get("dp_backend", "nccl"), tp_backend=a.get("tp_backend", "nccl"),
-                  ir_analyze=__import__("aicomp_b200").IR_Anal[a.get("ir", "PARALLEL")])
+                  ir_analyze=__import__("aicomp_b200").IR_Anal[a.get("ir", "PARALLEL")], dynamo_capture=a.get("dynamo", False),
+                  fused_kernels=False if a.get("dynamo") else None)
     opt = torch.optim.AdamW(e.parameters(), lr=a.get("lr", 1e-3))
     e.optimizer = opt
     losses = []
     for step in range(a.get("steps", 3)):
-        ids, labels = make_batch(a["model"], a.get("batch", 4), seed=step)
+        ids, labels = make_batch(a["model"], a.get("batch", 4), seed=step, seq=a.get("seq", 16))
         if e.tpl.dp_size > 1:  # each replica takes its slice of the global batch
             per = ids.shape[0] // e.tpl.dp_size
             sl = slice(e.tpl.dp_rank * per, (e.tpl.dp_rank + 1) * per)
