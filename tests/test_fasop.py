@@ -86,3 +86,23 @@ def test_profiledb_reads_reference_format(tmp_path):
     save_profile(str(tmp_path / "llama3b_B200_2.npz"), fwd, fwd * 1.7)
     f, b = ProfileDB(m, "B200", str(tmp_path)).node_times(2, 1)
     assert np.allclose(b, 1.7 * fwd[0] * 1e-3)
+
+
+def test_viewer_serves_page_and_data(tmp_path):
+    import json
+    import threading
+    import urllib.request
+    from aicomp_b200.fasop.viewer import serve
+    log = tmp_path / "r.jsonl"
+    run_strategy_search(FasopConfig([("B200", 8)], "llama3b", gbs=[128]), str(log))
+    srv, _ = serve(str(log), port=0)
+    port = srv.server_address[1]
+    t = threading.Thread(target=srv.serve_forever, daemon=True)
+    t.start()
+    try:
+        page = urllib.request.urlopen(f"http://127.0.0.1:{port}/", timeout=5).read().decode()
+        assert "FASOP" in page
+        data = json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/data", timeout=5).read())
+        assert data["meta"]["model"] == "llama3b" and len(data["rows"]) > 20
+    finally:
+        srv.shutdown()
