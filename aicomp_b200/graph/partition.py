@@ -37,7 +37,7 @@ log = get_logger(__name__)
 
 __all__ = ["assign_stages", "PARTITIONERS", "block_index_of"]
 
-PARTITIONERS = ("auto", "simple", "milp", "hierarchical", "llama-tp-split")
+PARTITIONERS = ("auto", "simple", "milp", "hierarchical", "llama-tp-split", "balanced")
 
 _BLOCK_RE = re.compile(r"(?:^|[._])(?:layers|h|layer|blocks|block)[._](\d+)(?:[._]|$)")
 
@@ -133,6 +133,64 @@ def assign_llama_tp_split(gm: fx.GraphModule, num_stage: int) -> Dict[fx.Node, i
         for b in range(bounds[s], bounds[s + 1]):
             stage_of_block[b] = s
     res = {n: stage_of_block[b] for n, b in zip(nodes, blocks)}
+    return _finalise(gm, res, num_stage)
+
+
+def assign_balanced(gm: fx.GraphModule, num_stage: int) -> Dict[fx.Node, int]:
+    """Contiguous split that minimises the heaviest stage, with a module's matmul parameter count as its cost.
+
+    For transformer stacks the FLOPs of a module are proportional to the parameters it multiplies with, so this
+    balances compute: the vocabulary projection counts as ~2.4 Llama-3-8B layers, the embedding lookup as nothing.
+    Exact dynamic programme over the positions after each ``call_module``.  Not in the reference, whose ``simple``
+    split counts modules (IR.py:1803-1966) and leaves the last stage with the head on top of an equal layer share.
+    """
+    nodes = _compute_nodes(gm)
+    mod_pos = [i for i, n in enumerate(nodes) if n.op == "call_module"]
+    if len(mod_pos) < num_stage:
+        raise ValueError("fewer modules than stages")
+    w = []
+    for i in mod_pos:
+        m = gm.get_submodule(str(nodes[i].target))
+        if "embedding" in type(m).__name__.lower():
+            w.append(0.0)
+        else:
+            w.append(float(sum(p.numel() for p in m.parameters() if p.dim() >= 2)) + 1.0)
+    n = len(w)
+    pre = [0.0]
+    for x in w:
+        pre.append(pre[-1] + x)
+    INF = float("inf")
+    best = [[INF] * (n + 1) for _ in range(num_stage + 1)]
+    back = [[0] * (n + 1) for _ in range(num_stage + 1)]
+    best[0][0] = 0.0
+    for s in range(1, num_stage + 1):
+        for j in range(s, n + 1):
+            for i in range(s - 1, j):
+                if best[s - 1][i] == INF:
+                    continue
+                v = max(best[s - 1][i], pre[j] - pre[i])
+                if v < best[s][j]:
+                    best[s][j], back[s][j] = v, i
+    cuts, j = [], n
+    for s in range(num_stage, 0, -1):
+        cuts.append(j)
+        j = back[s][j]
+    cuts = cuts[::-1]  # number of modules up to and including each stage
+    stage_of_mod = []
+    s = 0
+    for k in range(n):
+        while k >= cuts[s]:
+            s += 1
+        stage_of_mod.append(s)
+    res: Dict[fx.Node, int] = {}
+    cur, k = 0, 0
+    for i, node in enumerate(nodes):
+        if node.op == "call_module":
+            cur = stage_of_mod[k]
+            k += 1
+        res[node] = cur
+    # glue that follows a stage's last module (e.g. the residual add) stays with it: nodes take the stage of the
+    # most recent module, so only the glue BEFORE the first module of a stage needs pulling back
     return _finalise(gm, res, num_stage)
 
 
@@ -286,12 +344,16 @@ def assign_stages(gm: fx.GraphModule, num_stage: int, method: str = "auto", is_l
     if num_stage == 1:
         return {n: 0 for n in gm.graph.nodes}
     if method == "auto":
-        method = "llama-tp-split" if (is_llama and tp_size > 1) else "simple"
-    if is_llama and tp_size > 1 and method != "llama-tp-split":
+        fused_layers = any(n.op == "call_module" and type(gm.get_submodule(str(n.target))).__name__ == "B200LlamaLayer"
+                           for n in gm.graph.nodes)
+        method = "llama-tp-split" if (is_llama and tp_size > 1 and not fused_layers) else ("balanced" if fused_layers else "simple")
+    if is_llama and tp_size > 1 and method not in ("llama-tp-split", "balanced"):
         log.warning("Llama with tensor parallelism uses the 'llama-tp-split' partitioner (was %s)", method)
         method = "llama-tp-split"
     if method == "simple":
         return assign_simple(gm, num_stage)
+    if method == "balanced":
+        return assign_balanced(gm, num_stage)
     if method == "llama-tp-split":
         try:
             return assign_llama_tp_split(gm, num_stage)
