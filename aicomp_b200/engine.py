@@ -65,7 +65,8 @@ class Optimus_p:
                  # extensions of this framework
                  dtype: Optional[torch.dtype] = None, fused_kernels: Optional[bool] = None, sequence_parallel: bool = True,
                  dp_backend: str = "fused", tp_backend: str = "fused", example_inputs: Optional[Dict[str, Any]] = None,
-                 input_names: Optional[List[str]] = None, loss_fn=None, init_fn=None, trace_kwargs: Optional[Dict[str, Any]] = None):
+                 input_names: Optional[List[str]] = None, loss_fn=None, init_fn=None, trace_kwargs: Optional[Dict[str, Any]] = None,
+                 cuda_graphs: bool = False):
         self.comm = Comm(use_gpu=use_gpu)
         self.use_gpu = self.comm.use_gpu
         self.device = self.comm.device
@@ -166,6 +167,11 @@ class Optimus_p:
         self.label_group = None
 
         self._user_loss_fn = loss_fn
+        # CUDA-graph replay of a stage's per-micro-batch forward/backward (tensor-parallel stages stay eager: their
+        # peer-flag epochs advance on the host)
+        self.cuda_graphs = bool(cuda_graphs) and self.use_gpu and tp_size == 1 and not activation_ckpt and not preserve_output
+        self._graphed = None
+        self._graph_sig = None
         if checkpoint:
             post = ckpt_dir_postfix if ckpt_dir_postfix is not None else "None"
             self.ckpt_dir = f"checkpoint_{post}_{stage}"
@@ -188,6 +194,85 @@ class Optimus_p:
             return ops.cross_entropy(logits.reshape(-1, logits.shape[-1]), labels.reshape(-1), self.ignore_index, unit_grad=True)
         out = model_out[0] if isinstance(model_out, (tuple, list)) else model_out
         return F.mse_loss(out, labels)
+
+    def graphed_stage(self, mb: int, args, labels):
+        """Callable that replays this stage's captured forward (+loss) graph for micro-batch ``mb``, or None.
+
+        One captured instance per micro-batch that can be in flight at once (``pp_size - stage`` under 1F1B), built
+        with ``torch.cuda.make_graphed_callables`` on first use for the given input shapes; a change of shapes falls
+        back to eager execution.
+        """
+        if not self.cuda_graphs:
+            return None
+        last = self.tpl.is_last_stage()
+        if last and labels is None:
+            return None
+        sig = tuple((tuple(a.shape), a.dtype, bool(a.requires_grad)) if isinstance(a, torch.Tensor) else repr(a) for a in args)
+        if last:
+            sig = sig + ((tuple(labels.shape), labels.dtype),)
+        if self._graphed is None:
+            if not all(isinstance(a, torch.Tensor) for a in args):
+                self.cuda_graphs = False
+                return None
+            try:
+                self._build_graphs(args, labels)
+            except RuntimeError as exc:  # a capture rule was broken: keep training, eagerly
+                log.warning("CUDA-graph capture of stage %d failed (%s); running eagerly", self.tpl.stage, str(exc).splitlines()[0])
+                torch.cuda.synchronize()
+                self._graphed, self.cuda_graphs = None, False
+                self._reset_grad_state()
+                return None
+            self._graph_sig = sig
+        if sig != self._graph_sig or len(self._graphed) < self.schedule.in_flight():
+            return None
+        return self._graphed[mb % len(self._graphed)]
+
+    def _build_graphs(self, args, labels) -> None:
+        from .utils.stage_graphs import capture_stage_slots
+        last = self.tpl.is_last_stage()
+        inner = self.stage_module
+
+        def stage_fn(*flat):
+            if last:
+                out, outs = inner(*flat[:-1])
+                return (self.loss_fn(out, flat[-1]), *outs)
+            _, outs = inner(*flat)
+            return tuple(outs)
+
+        def sample():
+            out = []
+            for a in args:
+                t = torch.empty_like(a).copy_(a).detach()
+                if a.is_floating_point() and a.requires_grad:
+                    t.requires_grad_(True)
+                out.append(t)
+            if last:
+                out.append(labels.detach().clone())
+            return out
+
+        n_slots = self.schedule.in_flight()
+        launches0 = ops.launch_count()
+        slots = capture_stage_slots(stage_fn, sample, list(inner.parameters()), n_slots)
+        # two eager warm-up passes and one captured pass per slot: kernels of this library in one forward+backward
+        per_replay = (ops.launch_count() - launches0) // (3 * n_slots)
+
+        def counted(slot):
+            def call(*a):
+                ops.add_launches(per_replay)  # the replayed graphs hold these kernels; Python never sees them launch
+                res = slot(*a)
+                return res if isinstance(res, tuple) else (res,)
+            return call
+        self._graphed = tuple(counted(s) for s in slots)
+        self._reset_grad_state()
+
+    def _reset_grad_state(self) -> None:
+        """Warm-up and capture run real backward passes: drop what they accumulated."""
+        for p in self.stage_module.parameters():
+            mg = getattr(p, "main_grad", None)
+            if mg is not None:
+                mg.zero_()
+            p.grad = None
+            p.grad_accumulated = False
 
     def dp_sync_context(self, is_final: bool):
         return contextlib.nullcontext()

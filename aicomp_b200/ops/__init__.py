@@ -18,7 +18,7 @@ from ._lib import check_errors, have_gpu_kernels  # noqa: F401
 
 __all__ = [
     "gemm", "linear", "rmsnorm", "layernorm", "rope_inplace", "apply_rope_qkv", "swiglu", "gelu_tanh", "cross_entropy",
-    "embedding", "scaled_softmax", "check_errors", "have_gpu_kernels", "kernels_for", "launch_count", "reset_launch_count",
+    "embedding", "scaled_softmax", "check_errors", "have_gpu_kernels", "kernels_for", "launch_count", "reset_launch_count", "add_launches",
 ]
 
 GEMM_OUT_F32 = 1
@@ -31,6 +31,11 @@ _launches = 0
 def _count(n: int = 1) -> None:
     global _launches
     _launches += n
+
+
+def add_launches(n: int) -> None:
+    """Account for kernels of this library that run inside a replayed CUDA graph."""
+    _count(int(n))
 
 
 def launch_count() -> int:

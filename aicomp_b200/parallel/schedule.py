@@ -97,7 +97,19 @@ class Schedule:
                 if mb + 1 < self.M:
                     e.fwd_in.post_recv(first=False)
             args = [env[n] for n in self.plan.stage_inputs[self.stage]]
-            if e.activation_ckpt and not self.last:
+            loss = None
+            graphed = e.graphed_stage(mb, args, labels) if e.training else None
+            if graphed is not None:
+                # forward (and, on the last stage, the loss) replayed from a captured CUDA graph: two launches instead
+                # of the thousand-odd kernel launches Python would issue for this micro-batch
+                model_out = None
+                res = graphed(*args, labels) if self.last else graphed(*args)
+                res = res if isinstance(res, tuple) else (res,)
+                if self.last:
+                    loss, outs = res[0], res[1:]
+                else:
+                    outs = res
+            elif e.activation_ckpt and not self.last:
                 with torch.no_grad():
                     model_out, outs = e.stage_module(*args)
                 for t in outs:  # recomputed in backward; downstream must still return gradients for them
@@ -109,8 +121,7 @@ class Schedule:
             if not self.last:
                 payload = [env[n] for n in self.plan.send_names(self.stage)]
                 e.fwd_out.send(payload, first=(mb == 0))
-            loss = None
-            if self.last:
+            if self.last and graphed is None:
                 if labels is not None:
                     loss = e.loss_fn(model_out, labels)
                 if e.preserve_output:
@@ -160,6 +171,9 @@ class Schedule:
                 is_final = mb == self.order_last_backward
                 with e.dp_sync_context(is_final):
                     torch.autograd.backward(roots, root_grads)
+            if self.last and e.cuda_graphs:
+                # a replayed graph writes its loss into one static tensor per slot: keep this micro-batch's value
+                self.losses[mb] = self.losses[mb].detach().clone()
             for t, g in relayed:
                 t.grad = g if t.grad is None else t.grad + g
             if not self.first:
@@ -177,6 +191,10 @@ class Schedule:
     def order(self) -> List[tuple]:
         raise NotImplementedError
 
+    def in_flight(self) -> int:
+        """Largest number of micro-batches whose forward has run and whose backward has not."""
+        raise NotImplementedError
+
     def run(self, data, labels) -> None:
         e = self.e
         M = self.M
@@ -186,12 +204,17 @@ class Schedule:
         self.bwd_sent = 0
         e.outputs = [None] * M
         chunks, label_chunks = self.split_inputs(data, labels)
+        import os as _os
+        import time as _time
+        prof = StepProfile(e.device) if _os.environ.get("AICOMP_PROFILE_SCHEDULE") == "1" else None
+        t_run0 = _time.perf_counter()
         steps = self.order()
         self.order_last_backward = [mb for kind, mb in steps if kind == "B"][-1] if e.training else -1
         if not self.first:
             e.fwd_in.post_recv(first=True)
         posted_bwd = False
         for kind, mb in steps:
+            tok = prof.begin() if prof else None
             if kind == "F":
                 self.forward_step(mb, chunks[mb], label_chunks[mb])
             else:
@@ -199,12 +222,18 @@ class Schedule:
                     e.bwd_in.post_recv(first=True)
                     posted_bwd = True
                 self.backward_step(mb)
+            if prof:
+                prof.end(kind, tok)
         for ch in (e.fwd_out, e.bwd_out):
             if ch is not None:
                 ch.flush()
         e.losses = self.losses
         if e.training:
             e.dp_finish()
+        if prof:
+            out = prof.summary()
+            out["wall_ms"] = round(1e3 * (_time.perf_counter() - t_run0), 1)
+            print(f"[schedule profile] rank {e.comm.rank} stage {self.stage}: {out}", flush=True)
 
 
 def _detach_tree(x):
@@ -220,6 +249,9 @@ def _detach_tree(x):
 class ScheduleGPipe(Schedule):
     """All forwards, then all backwards."""
 
+    def in_flight(self) -> int:
+        return self.M
+
     def order(self):
         steps = [("F", i) for i in range(self.M)]
         if self.e.training:
@@ -229,6 +261,9 @@ class ScheduleGPipe(Schedule):
 
 class Schedule1F1B(Schedule):
     """Warm-up of ``P-1-stage`` forwards, then one-forward-one-backward, then the remaining backwards."""
+
+    def in_flight(self) -> int:
+        return max(1, min(self.P - self.stage, self.M))
 
     def order(self):
         if not self.e.training:
@@ -245,3 +280,40 @@ class Schedule1F1B(Schedule):
 
 
 SCHEDULES = {"gpipe": ScheduleGPipe, "1f1b": Schedule1F1B}
+
+
+class StepProfile:
+    """Optional per-step breakdown (``AICOMP_PROFILE_SCHEDULE=1``): device time inside forward / backward micro-steps
+    (CUDA events), host time spent issuing them, and the step's wall time, printed per rank."""
+
+    def __init__(self, device):
+        self.cuda = device.type == "cuda"
+        self.ev = []
+        self.host = {"F": 0.0, "B": 0.0}
+
+    def begin(self):
+        import time
+        if self.cuda:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+        else:
+            e = None
+        return e, time.perf_counter()
+
+    def end(self, kind, tok):
+        import time
+        e0, t0 = tok
+        self.host[kind] += time.perf_counter() - t0
+        if self.cuda:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record()
+            self.ev.append((kind, e0, e1))
+
+    def summary(self):
+        dev = {"F": 0.0, "B": 0.0}
+        if self.cuda:
+            torch.cuda.synchronize()
+            for k, a, b in self.ev:
+                dev[k] += a.elapsed_time(b)
+        return {"dev_F_ms": round(dev["F"], 1), "dev_B_ms": round(dev["B"], 1), "host_F_ms": round(1e3 * self.host["F"], 1),
+                "host_B_ms": round(1e3 * self.host["B"], 1)}

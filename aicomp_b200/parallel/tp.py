@@ -42,6 +42,6 @@ def finish_sequence_parallel_grads(stage_module: nn.Module, tpl) -> None:
         return
     for p in stage_module.parameters():
         if getattr(p, "sequence_parallel", False):
-            g = getattr(p, "main_grad", None) if getattr(p, "grad_accumulated", False) else p.grad
+            g = p.grad if p.grad is not None else getattr(p, "main_grad", None)
             if g is not None:
                 dist.all_reduce(g, group=tpl.tp_group)

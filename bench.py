@@ -35,6 +35,7 @@ def parse():
     ap.add_argument("--seqs-per-gpu", type=int, default=8)
     ap.add_argument("--dp-backend", default="fused")
     ap.add_argument("--attn", default="auto")
+    ap.add_argument("--no-graphs", action="store_true", help="issue every kernel from Python instead of replaying CUDA graphs")
     return ap.parse_args()
 
 
@@ -103,7 +104,7 @@ def run_ours(a):
     seqs_per_replica = a.seqs_per_gpu * a.gpus // dp
     num_mb = seqs_per_replica  # micro-batch 1
     eng = Optimus_p(model, num_mb=num_mb, use_gpu=True, pp_size=pp, dp_size=dp, tp_size=1, dtype=torch.bfloat16,
-                    dp_backend=a.dp_backend)
+                    dp_backend=a.dp_backend, cuda_graphs=not a.no_graphs)
     dev = eng.device
     opt = FusedAdamW(eng.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1, grad_scale=1.0 / num_mb, max_grad_norm=1.0,
                      norm_groups={"pp": eng.tpl.pp_group})
