@@ -66,7 +66,7 @@ class Optimus_p:
                  dtype: Optional[torch.dtype] = None, fused_kernels: Optional[bool] = None, sequence_parallel: bool = True,
                  dp_backend: str = "fused", tp_backend: str = "fused", example_inputs: Optional[Dict[str, Any]] = None,
                  input_names: Optional[List[str]] = None, loss_fn=None, init_fn=None, trace_kwargs: Optional[Dict[str, Any]] = None,
-                 cuda_graphs: bool = False):
+                 cuda_graphs: bool = False, pp_backend: str = "auto"):
         self.comm = Comm(use_gpu=use_gpu)
         self.use_gpu = self.comm.use_gpu
         self.device = self.comm.device
@@ -158,12 +158,14 @@ class Optimus_p:
         self.fwd_in = self.fwd_out = self.bwd_in = self.bwd_out = None
         if pp_size > 1:
             prev, nxt = self.tpl.get_prev_rank(), self.tpl.get_next_rank()
+            pb = self._pick_pp_backend(pp_backend)
+            self.pp_backend = pb
             if prev is not None:
-                self.fwd_in = self.comm.make_channel(prev, self.comm.rank, f"fwd{stage - 1}", self.tpl.fwd_groups[stage - 1])
-                self.bwd_out = self.comm.make_channel(self.comm.rank, prev, f"bwd{stage - 1}", self.tpl.bwd_groups[stage - 1])
+                self.fwd_in = self.comm.make_channel(prev, self.comm.rank, f"fwd{stage - 1}", self.tpl.fwd_groups[stage - 1], pb)
+                self.bwd_out = self.comm.make_channel(self.comm.rank, prev, f"bwd{stage - 1}", self.tpl.bwd_groups[stage - 1], pb)
             if nxt is not None:
-                self.fwd_out = self.comm.make_channel(self.comm.rank, nxt, f"fwd{stage}", self.tpl.fwd_groups[stage])
-                self.bwd_in = self.comm.make_channel(nxt, self.comm.rank, f"bwd{stage}", self.tpl.bwd_groups[stage])
+                self.fwd_out = self.comm.make_channel(self.comm.rank, nxt, f"fwd{stage}", self.tpl.fwd_groups[stage], pb)
+                self.bwd_in = self.comm.make_channel(nxt, self.comm.rank, f"bwd{stage}", self.tpl.bwd_groups[stage], pb)
         self.label_group = None
 
         self._user_loss_fn = loss_fn
@@ -194,6 +196,21 @@ class Optimus_p:
             return ops.cross_entropy(logits.reshape(-1, logits.shape[-1]), labels.reshape(-1), self.ignore_index, unit_grad=True)
         out = model_out[0] if isinstance(model_out, (tuple, list)) else model_out
         return F.mse_loss(out, labels)
+
+    def _pick_pp_backend(self, requested: str) -> str:
+        """Transport between neighbouring stages: 'peer' (copy engines + flags in peer-mapped memory) when every rank
+        of the job sits on this node's GPUs, else the process group's ``isend``/``irecv``."""
+        requested = os.environ.get("AICOMP_PP_BACKEND", requested)
+        if requested not in ("auto", "peer", "nccl"):
+            raise ValueError("pp_backend must be 'auto', 'peer' or 'nccl'")
+        if requested == "nccl" or self.device.type != "cuda":
+            return "nccl"
+        from .parallel.p2p import peer_transport_available
+        one_node = int(os.environ.get("LOCAL_WORLD_SIZE", "0")) == self.comm.world_size
+        ok = peer_transport_available(self.device) and one_node
+        if requested == "peer" and not ok:
+            raise RuntimeError("pp_backend='peer' needs CUDA, the kernel library and all ranks on one node")
+        return "peer" if ok else "nccl"
 
     def graphed_stage(self, mb: int, args, labels):
         """Callable that replays this stage's captured forward (+loss) graph for micro-batch ``mb``, or None.

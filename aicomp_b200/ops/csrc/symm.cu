@@ -16,6 +16,7 @@
 //
 // The reference moves gradients with NCCL all-reduce inside torch DDP
 // (opt_prime/opt_prime/opti_pri.py:852) and has no KV transfer at all.
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
@@ -286,4 +287,44 @@ extern "C" int b200_sum_parts_bf16(const void* in, int parts, long long part_str
   b200::sum_parts_bf16_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(static_cast<const uint4*>(in), parts, part_stride_elems / 8,
                                                                           static_cast<uint4*>(out), n16);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// ---------------------------------------------------------------- stream-ordered mailbox primitives (pipeline P2P)
+// A pipeline stage hands a micro-batch to its neighbour by copying it into a ring slot in the neighbour's memory
+// (copy engine, no SMs) and then storing the message number into a flag beside the slot; the neighbour's stream waits
+// for the flag with a stream memory operation, which holds no SM either.  A receive that is posted early therefore
+// takes no resources away from the persistent GEMM kernels that run while it is pending, unlike a receive kernel.
+__global__ void store_flag_kernel(uint32_t* flag, uint32_t value) {
+  __threadfence_system();
+  st_release_sys(flag, value);
+}
+// *flag = value (flag may live in a peer's memory), ordered after all earlier work of the stream.
+extern "C" int b200_stream_store_flag(void* flag, unsigned int value, cudaStream_t stream) {
+  store_flag_kernel<<<1, 1, 0, stream>>>(static_cast<uint32_t*>(flag), value);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+typedef CUresult (*StreamWaitValue32Fn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+static StreamWaitValue32Fn get_wait_value_fn() {
+  static StreamWaitValue32Fn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuStreamWaitValue32", &ptr, cudaEnableDefault, &q) != cudaSuccess || !ptr) return nullptr;
+    fn = reinterpret_cast<StreamWaitValue32Fn>(ptr);
+  }
+  return fn;
+}
+// Later work of `stream` runs once (int32)(*flag - value) >= 0.  `flag` is in THIS device's memory (a peer stores
+// into it).  The wait occupies no SM; it ends when the flag arrives or the owning process exits.
+extern "C" int b200_stream_wait_flag_geq(void* flag, unsigned int value, cudaStream_t stream) {
+  StreamWaitValue32Fn fn = get_wait_value_fn();
+  if (!fn) return -1;
+  CUresult r = fn(reinterpret_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(flag), value, CU_STREAM_WAIT_VALUE_GEQ);
+  return r == CUDA_SUCCESS ? 0 : -2000 - static_cast<int>(r);
+}
+// Device-to-device copy by the copy engines; either side may be a peer mapping.
+extern "C" int b200_copy_async(void* dst, const void* src, long long bytes, cudaStream_t stream) {
+  if (bytes <= 0) return 0;
+  return cudaMemcpyAsync(dst, src, static_cast<size_t>(bytes), cudaMemcpyDeviceToDevice, stream) == cudaSuccess ? 0 : -4;
 }

@@ -148,7 +148,12 @@ class Comm:
         return _decode(header, tensors)
 
     # ------------------------------------------------------------------ channels
-    def make_channel(self, src: int, dst: int, tag: str, group=None) -> "Channel":
+    def make_channel(self, src: int, dst: int, tag: str, group=None, backend: str = "nccl") -> "Channel":
+        """``backend='peer'``: ring in the receiver's memory written by the sender's copy engines (one node, CUDA);
+        ``'nccl'``: ``isend``/``irecv`` of the process group (any backend, any topology)."""
+        if backend == "peer":
+            from .p2p import PeerChannel
+            return PeerChannel(self, src, dst, tag, group)
         return Channel(self, src, dst, tag, group)
 
 

@@ -13,8 +13,9 @@ It differs from ``torch.cuda.make_graphed_callables`` where a pipeline needs it 
 * warm-up and capture run on ONE side stream, so gradient-accumulator nodes created during warm-up belong to the
   capturing stream and the autograd engine has no second stream to order against (with two streams it records an
   event on the uncaptured one and the capture fails with ``cudaErrorStreamCaptureIsolation``);
-* gradients handed back for the stage inputs are copies: the pipeline sends them asynchronously to the previous stage,
-  and the next replay of the slot must not overwrite a gradient that is still being sent.
+* gradients handed back to autograd are copies of the static buffers: the pipeline sends input gradients
+  asynchronously to the previous stage, and autograd may keep a parameter gradient as ``.grad``; the next replay of
+  the slot must overwrite neither.
 
 Parameters that accumulate into ``main_grad`` inside their own backward kernels return no gradient to autograd; any
 other parameter's gradient comes back through the replay function and is accumulated into ``.grad`` by autograd as in
@@ -65,8 +66,9 @@ class _Replay(torch.autograd.Function):
             if g is None:
                 out.append(None)
             else:
-                # activation gradients leave through an asynchronous send: hand out a copy, the slot replays again
-                out.append(g.clone() if i < ctx.n_args else g.detach())
+                # always a copy: activation gradients leave through an asynchronous send while the slot replays again,
+                # and autograd may adopt a parameter gradient as ``.grad`` itself, which the next replay would overwrite
+                out.append(g.clone())
         return (None, None, *out)
 
 

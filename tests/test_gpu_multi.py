@@ -50,3 +50,23 @@ def test_tp2_training_fused_matches_nccl_backend():
     b = run_workers("train_worker", 2, dict(base, tp_backend="fused"), timeout=300, env_extra={"NCCL_NVLS_ENABLE": "0"})
     for x, y in zip(a[0]["losses"], b[0]["losses"]):
         assert abs(x - y) < 3e-2 * abs(x), (a[0]["losses"], b[0]["losses"])
+
+
+def test_pp2_peer_transport_and_graph_replay_match_nccl_eager():
+    """Pipeline over the peer-memory mailbox, with and without CUDA-graph replay of the stages, against NCCL isend/irecv."""
+    _need(2)
+    base = {"model": "llama_d128", "pp": 2, "num_mb": 4, "steps": 4, "batch": 8, "use_gpu": True, "dtype": "bfloat16", "seq": 256}
+    env = {"NCCL_NVLS_ENABLE": "0"}
+    ref = run_workers("train_worker", 2, dict(base, pp_backend="nccl"), timeout=300, env_extra=env)
+    runs = {"peer": run_workers("train_worker", 2, dict(base, pp_backend="peer"), timeout=300, env_extra=env),
+            "peer+graphs": run_workers("train_worker", 2, dict(base, pp_backend="peer", graphs=True), timeout=300, env_extra=env),
+            "peer+graphs gpipe": run_workers("train_worker", 2, dict(base, pp_backend="peer", graphs=True, mode="gpipe"), timeout=300,
+                                             env_extra=env)}
+    want = [r["losses"] for r in ref if r["losses"][0] is not None][0]
+    for name, res in runs.items():
+        assert all(r["pp_backend"] == "peer" for r in res), name
+        if "graphs" in name:
+            assert all(r["graphs"] for r in res), f"{name}: capture fell back to eager"
+        got = [r["losses"] for r in res if r["losses"][0] is not None][0]
+        for x, y in zip(want, got):
+            assert abs(x - y) < 2e-2 * abs(x), (name, want, got)

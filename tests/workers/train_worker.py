@@ -21,7 +21,8 @@ def main():
                   dtype=getattr(torch, a["dtype"]) if a.get("dtype") else None, sequence_parallel=a.get("sp", True),
                   dp_backend=a.get("dp_backend", "nccl"), tp_backend=a.get("tp_backend", "nccl"),
                   ir_analyze=__import__("aicomp_b200").IR_Anal[a.get("ir", "PARALLEL")], dynamo_capture=a.get("dynamo", False),
-                  fused_kernels=False if a.get("dynamo") else None)
+                  fused_kernels=False if a.get("dynamo") else None, cuda_graphs=a.get("graphs", False),
+                  pp_backend=a.get("pp_backend", "auto"))
     opt = torch.optim.AdamW(e.parameters(), lr=a.get("lr", 1e-3))
     e.optimizer = opt
     losses = []
@@ -40,7 +41,7 @@ def main():
         l = e.get_loss()
         losses.append(sum(l) / len(l) if l is not None else None)
     checksum = float(sum(p.detach().double().abs().sum().item() for p in e.parameters()))
-    worker_report({"losses": losses, "stage": e.tpl.stage, "dp_rank": e.tpl.dp_rank, "tp_rank": e.tpl.tp_rank,
+    worker_report({"losses": losses, "pp_backend": getattr(e, "pp_backend", None), "graphs": bool(e.cuda_graphs and e._graphed), "stage": e.tpl.stage, "dp_rank": e.tpl.dp_rank, "tp_rank": e.tpl.tp_rank,
                    "checksum": checksum, "n_params": sum(p.numel() for p in e.parameters())})
     e.comm.barrier()
 
