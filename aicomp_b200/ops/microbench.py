@@ -70,9 +70,45 @@ def bench_gemm(shapes=None):
         del a, b, out
 
 
+def small_case(kind: str, launches: int = 3) -> None:
+    """A few launches of one kernel on inputs larger than L2 and well under 2 GB: the case a profiler captures."""
+    dev = "cuda"
+    if kind == "gemm":      # gate_up forward of Llama-3-8B on 8192 tokens: A 64 MB, B 224 MB, C 448 MB
+        a = torch.randn(8192, 4096, device=dev, dtype=torch.bfloat16)
+        b = torch.randn(28672, 4096, device=dev, dtype=torch.bfloat16)
+        out = torch.empty(8192, 28672, device=dev, dtype=torch.bfloat16)
+        fn = lambda: ops.gemm(a, b, out=out, bn=256)
+        work = 2.0 * 8192 * 28672 * 4096
+    elif kind == "wgrad":   # gate_up weight gradient, fp32 accumulate in memory (TMA reduce-add epilogue)
+        x = torch.randn(8192, 4096, device=dev, dtype=torch.bfloat16)
+        dy = torch.randn(8192, 28672, device=dev, dtype=torch.bfloat16)
+        out = torch.zeros(28672, 4096, device=dev, dtype=torch.float32)
+        fn = lambda: ops.gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=True, bn=256)
+        work = 2.0 * 8192 * 28672 * 4096
+    elif kind == "flash":   # causal attention forward on packed QKV: 8 x 4096 tokens, 32 query / 8 KV heads of 128
+        from aicomp_b200.ops import flash
+        qkv = torch.randn(8 * 4096, (32 + 16) * 128, device=dev, dtype=torch.bfloat16)
+        fn = lambda: flash.flash_fwd(qkv, 8, 4096, 32, 8, 128)
+        work = 4.0 * 8 * 32 * 4096 * 4096 * 128 / 2
+    elif kind == "rmsnorm":  # 65536 x 4096 bf16: 512 MB in, 512 MB out
+        x = torch.randn(65536, 4096, device=dev, dtype=torch.bfloat16)
+        w = torch.ones(4096, device=dev, dtype=torch.bfloat16)
+        fn = lambda: ops.rmsnorm(x, w, 1e-5)
+        work = 2.0 * x.numel() * 2
+    else:
+        raise SystemExit(f"unknown small case {kind}")
+    with torch.no_grad():
+        t = _time(fn, iters=launches, warmup=2)
+    ops.check_errors()
+    print(json.dumps({"case": kind, "ms": round(t, 4), "work_per_s": round(work / t / 1e9, 1),
+                      "unit": "GB/s" if kind == "rmsnorm" else "TFLOP/s"}), flush=True)
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     if what == "gemm":
         bench_gemm()
+    elif what == "small":
+        small_case(sys.argv[2] if len(sys.argv) > 2 else "gemm")
     else:
         raise SystemExit(f"unknown benchmark {what}")
