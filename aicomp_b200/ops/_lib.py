@@ -133,7 +133,8 @@ def err_word(device: torch.device) -> torch.Tensor:
 
 
 _ERR_NAMES = {1: "consumer wait for TMA stage", 2: "producer wait for free stage", 3: "epilogue wait for accumulator",
-              4: "MMA wait for drained accumulator", 5: "wait for a peer GPU's flag", 6: "bad argument"}
+              4: "MMA wait for drained accumulator", 5: "wait for a peer GPU's flag", 6: "bad argument",
+              7: "dynamic shared memory window not 1024-byte aligned"}
 
 
 def check_errors(device: Optional[torch.device] = None) -> None:

@@ -2,13 +2,15 @@
 //
 // Reads q, k, v straight out of the packed QKV projection [tokens, (Hq + 2 Hkv) * 128] through ONE tiled TMA
 // descriptor (box 64 x 128, 128-byte swizzle), so there is no transpose, no repeat_kv and no padding copy.
-// One CTA = 128 query rows of one (batch, head).  Roles (192 threads):
+// One CTA = 128 query rows of one (batch, head).  Roles (320 threads):
 //   warp 0      TMA producer: Q once, then K_j / V_j tiles of 128 keys into two-deep rings;
 //   warp 1      MMA issuer:  S_j = Q K_j^T  (SS MMA, 128x128x16 x8)  into one of two TMEM score buffers,
 //               then O += P_j V_j with P_j read from shared memory; S_{j+1} is issued before P_j V_j so the
 //               tensor core works on the next scores while the softmax warps are busy;
-//   warps 2-5   softmax: thread = query row.  tcgen05.ld brings the row's 128 scores, online softmax in the
-//               log2 domain, P_j is written as bf16 into a 128B-swizzled K-major tile (double buffered), and the
+//   warps 2-9   softmax: two warps per TMEM lane quadrant, each thread owns 64 of its query row's 128 scores
+//               (tcgen05.ld into registers once), the pair exchanges row maxima through shared memory, online
+//               softmax in the log2 domain, P_j is written as bf16 into a 128B-swizzled K-major tile (double
+//               buffered), and the
 //               accumulator O in TMEM is rescaled only when the running max moved by more than 2^8 (the stale
 //               max keeps exp2 arguments small; the final 1/l normalisation makes it exact).
 // Output: O [tokens, Hq * 128] bf16 and the log-sum-exp per (batch, head, row) for the backward pass.
@@ -22,7 +24,7 @@ namespace b200 {
 constexpr int FA_BM = 128;   // query rows per CTA
 constexpr int FA_BN = 128;   // keys per tile
 constexpr int FA_D = 128;
-constexpr int FA_THREADS = 192;
+constexpr int FA_THREADS = 320;         // TMA warp, MMA warp, eight softmax warps
 constexpr int FA_TILE_BYTES = FA_BM * FA_D * 2;       // 32 KB: two 64-column halves of 16 KB
 constexpr int FA_HALF_BYTES = FA_TILE_BYTES / 2;
 constexpr float FA_RESCALE_THRESHOLD = 8.0f;          // log2 units
@@ -43,13 +45,18 @@ struct FlashSmem {
   static constexpr int V_OFF = K_OFF + 2 * FA_TILE_BYTES;
   static constexpr int P_OFF = V_OFF + 2 * FA_TILE_BYTES;
   static constexpr int BAR_OFF = P_OFF + 2 * FA_TILE_BYTES;
-  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+  static constexpr int XCHG_OFF = BAR_OFF + 256;              // 4 x 128 floats: half-row maxima / sums [2 parities][2 groups]
+  static constexpr int TOTAL = XCHG_OFF + 4 * FA_BM * 4;      // 231,680 B: the dynamic window itself is 1024-byte aligned
 };
 
 __global__ void __launch_bounds__(FA_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, FlashArgs p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {  // the swizzled tiles need 1024-byte alignment; no static shared memory precedes the window
+    if (threadIdx.x == 0) atomicCAS(p.err, 0, ERR_BAD_ALIGNMENT);
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FlashSmem::BAR_OFF);
   uint64_t* q_full = bars;            // 1
   uint64_t* k_full = bars + 1;        // 2
@@ -61,8 +68,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, FlashArgs p) {
   uint64_t* p_full = bars + 13;       // 2 (count 4)
   uint64_t* p_empty = bars + 15;      // 2 (PV MMA that read P buffer b has completed)
   uint64_t* o_done = bars + 17;       // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
-  __shared__ int cta_abort;
+  uint64_t* pair_bar = bars + 18;     // 4 (count 64: the two warps that share a TMEM lane quadrant)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 22);
+  volatile int& cta_abort = *reinterpret_cast<volatile int*>(bars + 23);
+  float* xchg = reinterpret_cast<float*>(smem + FlashSmem::XCHG_OFF);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qblk = (p.S + FA_BM - 1) / FA_BM;
@@ -83,9 +92,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, FlashArgs p) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
-      mbar_init(&p_full[i], 4); mbar_init(&p_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 8);
+      mbar_init(&p_full[i], 8); mbar_init(&p_empty[i], 1);
     }
+    for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 64);
     mbar_init(o_done, 1);
     fence_barrier_init();
     prefetch_tmap(&tmQKV);
@@ -169,14 +179,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, FlashArgs p) {
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------ softmax / correction / epilogue: thread = query row
+    // ------------------------------------------------ softmax / correction / epilogue
+    // Two warps per TMEM lane quadrant (so every scheduler has two softmax warps to switch between): the warp of
+    // group `wg` owns columns [64 wg, 64 wg + 64) of each of its 32 query rows.  The pair exchanges the row maximum
+    // (and, at the end, the row sum) through shared memory, synchronised by a bounded mbarrier wait.
     const int quad = warp & 3;
+    const int wg = (warp - 2) >> 2;
     const int r = quad * 32 + lane;          // row inside the tile
     const int qi = q0 + r;                   // query position inside the sequence
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const int sw = r & 7;
+    const int colbase = wg * 64;
     float m_used = -CUDART_INF_F;            // max used for the exponentials so far (log2 domain)
-    float l = 0.f;
+    float l = 0.f;                           // sum over this warp's columns only
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       const int b = j & 1;
@@ -185,26 +200,32 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, FlashArgs p) {
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t tS = tmem_S0 + b * FA_BN + lane_addr;
-      const int kv0 = j * FA_BN;
-      const bool need_mask = (p.causal && kv0 + FA_BN > q0) || (kv0 + FA_BN > p.S);
-      // pass 1: row maximum
-      float mx = -CUDART_INF_F;
-#pragma unroll 1
-      for (int c = 0; c < FA_BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + c * 32, v);
-        tmem_ld_wait();
+      const uint32_t tS = tmem_S0 + b * FA_BN + lane_addr + colbase;
+      const int kv0 = j * FA_BN + colbase;
+      const bool need_mask = (p.causal && j * FA_BN + FA_BN > q0) || (j * FA_BN + FA_BN > p.S);
+      uint32_t v0[32], v1[32];
+      tmem_ld_32x32(tS, v0);
+      tmem_ld_32x32(tS + 32, v1);
+      tmem_ld_wait();
+      if (need_mask) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]);
-          if (need_mask) {
-            const int kj = kv0 + c * 32 + i;
-            if (kj >= p.S || (p.causal && kj > qi)) s = -CUDART_INF_F;
-          }
-          mx = fmaxf(mx, s);
+          const int k0 = kv0 + i, k1 = kv0 + 32 + i;
+          if (k0 >= p.S || (p.causal && k0 > qi)) v0[i] = 0xff800000u;
+          if (k1 >= p.S || (p.causal && k1 > qi)) v1[i] = 0xff800000u;
         }
       }
+      float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+      for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], fmaxf(__uint_as_float(v0[i]), __uint_as_float(v1[i])));
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // exchange the half-row maxima
+      xchg[(b * 2 + wg) * FA_BM + r] = mx;
+      mbar_arrive(&pair_bar[quad]);
+      ok = mbar_wait(&pair_bar[quad], j & 1, p.err, ERR_WAIT_FULL, &cta_abort);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      mx = fmaxf(mx, xchg[(b * 2 + (wg ^ 1)) * FA_BM + r]);
       const float m_cand = mx * p.scale_log2;
       float m_new = m_used;
       bool rescale = false;
@@ -226,50 +247,45 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, FlashArgs p) {
         tc_fence_after_sync();
         const float alpha = rescale ? exp2f(m_used - m_new) : 1.f;
 #pragma unroll 1
-        for (int c = 0; c < FA_D / 32; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t v[32];
-          tmem_ld_32x32(tmem_O + lane_addr + c * 32, v);
+          tmem_ld_32x32(tmem_O + lane_addr + colbase + c * 32, v);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-          tmem_st_32x32(tmem_O + lane_addr + c * 32, v);
+          tmem_st_32x32(tmem_O + lane_addr + colbase + c * 32, v);
         }
         tmem_st_wait();
         l *= alpha;
       }
       m_used = m_new;
-      // pass 2: exponentials, row sum, bf16 P into the swizzled K-major tile
-      uint8_t* sP = smem + FlashSmem::P_OFF + b * FA_TILE_BYTES;
-      float rowsum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < FA_BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + c * 32, v);
-        tmem_ld_wait();
-        float e[32];
+      const float msub = (m_used == -CUDART_INF_F) ? 0.f : m_used;
+      // exponentials, row sum, bf16 P into this group's 64-column half of the swizzled K-major tile
+      uint8_t* prow = smem + FlashSmem::P_OFF + b * FA_TILE_BYTES + wg * FA_HALF_BYTES + r * 128;
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]) * p.scale_log2 - (m_used == -CUDART_INF_F ? 0.f : m_used);
-          if (need_mask) {
-            const int kj = kv0 + c * 32 + i;
-            if (kj >= p.S || (p.causal && kj > qi)) s = -CUDART_INF_F;
-          }
-          e[i] = exp2f(s);
-          rowsum += e[i];
-        }
-        uint8_t* half = sP + (c >> 1) * FA_HALF_BYTES + r * 128;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 o;
-          o.x = pack_bf16x2(e[8 * g], e[8 * g + 1]);
-          o.y = pack_bf16x2(e[8 * g + 2], e[8 * g + 3]);
-          o.z = pack_bf16x2(e[8 * g + 4], e[8 * g + 5]);
-          o.w = pack_bf16x2(e[8 * g + 6], e[8 * g + 7]);
-          const int chunk = (c & 1) * 4 + g;
-          *reinterpret_cast<uint4*>(half + ((chunk ^ sw) << 4)) = o;
-        }
+      for (int i = 0; i < 32; ++i) {
+        const float e0 = exp2f(fmaf(__uint_as_float(v0[i]), p.scale_log2, -msub));
+        const float e1 = exp2f(fmaf(__uint_as_float(v1[i]), p.scale_log2, -msub));
+        rs4[i & 3] += e0 + e1;
+        v0[i] = __float_as_uint(e0);
+        v1[i] = __float_as_uint(e1);
       }
-      l += rowsum;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint4 o;
+        o.x = pack_bf16x2(__uint_as_float(v0[8 * g]), __uint_as_float(v0[8 * g + 1]));
+        o.y = pack_bf16x2(__uint_as_float(v0[8 * g + 2]), __uint_as_float(v0[8 * g + 3]));
+        o.z = pack_bf16x2(__uint_as_float(v0[8 * g + 4]), __uint_as_float(v0[8 * g + 5]));
+        o.w = pack_bf16x2(__uint_as_float(v0[8 * g + 6]), __uint_as_float(v0[8 * g + 7]));
+        *reinterpret_cast<uint4*>(prow + ((g ^ sw) << 4)) = o;
+        o.x = pack_bf16x2(__uint_as_float(v1[8 * g]), __uint_as_float(v1[8 * g + 1]));
+        o.y = pack_bf16x2(__uint_as_float(v1[8 * g + 2]), __uint_as_float(v1[8 * g + 3]));
+        o.z = pack_bf16x2(__uint_as_float(v1[8 * g + 4]), __uint_as_float(v1[8 * g + 5]));
+        o.w = pack_bf16x2(__uint_as_float(v1[8 * g + 6]), __uint_as_float(v1[8 * g + 7]));
+        *reinterpret_cast<uint4*>(prow + (((4 + g) ^ sw) << 4)) = o;
+      }
+      l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
       tc_fence_before_sync();
       fence_proxy_async_smem();
       __syncwarp();
@@ -283,16 +299,24 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, FlashArgs p) {
       ok = mbar_wait(o_done, 0, p.err, ERR_WAIT_TMEM_FULL, &cta_abort);
       ok = __all_sync(0xffffffffu, ok);
     }
+    if (ok) {   // total row sum = the pair's two partial sums
+      const int fb = n_kv & 1;  // the maxima slots of this parity were last read two tiles ago
+      xchg[(fb * 2 + wg) * FA_BM + r] = l;
+      mbar_arrive(&pair_bar[quad]);
+      ok = mbar_wait(&pair_bar[quad], n_kv & 1, p.err, ERR_WAIT_FULL, &cta_abort);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) l += xchg[((n_kv & 1) * 2 + (wg ^ 1)) * FA_BM + r];
+    }
     if (ok) {
       tc_fence_after_sync();
       const float inv_l = l > 0.f ? 1.f / l : 0.f;
       const bool row_ok = qi < p.S;
-      __nv_bfloat16* dst = p.out + static_cast<long long>(row_base + qi) * p.out_stride + head * FA_D;
+      __nv_bfloat16* dst = p.out + static_cast<long long>(row_base + qi) * p.out_stride + head * FA_D + colbase;
 #pragma unroll 1
-      for (int c = 0; c < FA_D / 32; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
         if (n_kv > 0) {
-          tmem_ld_32x32(tmem_O + lane_addr + c * 32, v);
+          tmem_ld_32x32(tmem_O + lane_addr + colbase + c * 32, v);
           tmem_ld_wait();
         } else {
 #pragma unroll
@@ -310,7 +334,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, FlashArgs p) {
           }
         }
       }
-      if (p.lse && row_ok)
+      if (p.lse && row_ok && wg == 0)
         p.lse[(static_cast<long long>(batch) * p.Hq + head) * p.S + qi] = (l > 0.f) ? (m_used + log2f(l)) * 0.6931471805599453f : -CUDART_INF_F;
     }
   }

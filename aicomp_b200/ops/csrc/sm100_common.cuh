@@ -23,6 +23,7 @@ enum ErrCode : int {
   ERR_WAIT_TMEM_EMPTY = 4, // MMA warp gave up waiting for a drained accumulator
   ERR_WAIT_PEER = 5,       // wait on a flag written by another GPU ran out
   ERR_BAD_ARG = 6,
+  ERR_BAD_ALIGNMENT = 7,   // the dynamic shared-memory window is not 1024-byte aligned
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

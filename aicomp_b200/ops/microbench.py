@@ -70,6 +70,38 @@ def bench_gemm(shapes=None):
         del a, b, out
 
 
+def bench_attention(shapes=None):
+    """Causal attention forward and backward of this library against torch SDPA (cuDNN / flash) on the same data."""
+    import torch.nn.functional as F
+
+    from aicomp_b200.ops import flash
+    dev = "cuda"
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    for (B, S, hq, hkv) in shapes or [(1, 2048, 32, 8), (4, 2048, 32, 8), (2, 4096, 32, 8), (1, 8192, 32, 8)]:
+        D = 128
+        qkv = torch.randn(B * S, (hq + 2 * hkv) * D, device=dev, dtype=torch.bfloat16)
+        dout = torch.randn(B * S, hq * D, device=dev, dtype=torch.bfloat16)
+        fwd_flops = 4.0 * B * hq * S * S * D / 2
+        res = {"B": B, "S": S, "hq": hq, "hkv": hkv}
+        out, lse = flash.flash_fwd(qkv, B, S, hq, hkv, D, need_lse=True)
+        t = _time(lambda: flash.flash_fwd(qkv, B, S, hq, hkv, D, need_lse=True), flush=flush)
+        res["ours_fwd_ms"], res["ours_fwd_tflops"] = round(t, 4), round(fwd_flops / t / 1e9, 1)
+        t = _time(lambda: flash.flash_bwd(qkv, out, dout, lse, B, S, hq, hkv, D), flush=flush)
+        res["ours_bwd_ms"], res["ours_bwd_tflops"] = round(t, 4), round(2.5 * fwd_flops / t / 1e9, 1)
+        q = qkv[:, : hq * D].view(B, S, hq, D).transpose(1, 2).detach().requires_grad_(True)
+        k = qkv[:, hq * D:(hq + hkv) * D].view(B, S, hkv, D).transpose(1, 2).detach().requires_grad_(True)
+        v = qkv[:, (hq + hkv) * D:].view(B, S, hkv, D).transpose(1, 2).detach().requires_grad_(True)
+        do4 = dout.view(B, S, hq, D).transpose(1, 2)
+        with torch.no_grad():
+            t = _time(lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True), flush=flush)
+        res["sdpa_fwd_ms"], res["sdpa_fwd_tflops"] = round(t, 4), round(fwd_flops / t / 1e9, 1)
+        o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+        t = _time(lambda: torch.autograd.grad(o, (q, k, v), do4, retain_graph=True), flush=flush)
+        res["sdpa_bwd_ms"], res["sdpa_bwd_tflops"] = round(t, 4), round(2.5 * fwd_flops / t / 1e9, 1)
+        ops.check_errors()
+        print(json.dumps(res), flush=True)
+
+
 def small_case(kind: str, launches: int = 3) -> None:
     """A few launches of one kernel on inputs larger than L2 and well under 2 GB: the case a profiler captures."""
     dev = "cuda"
@@ -90,6 +122,14 @@ def small_case(kind: str, launches: int = 3) -> None:
         qkv = torch.randn(8 * 4096, (32 + 16) * 128, device=dev, dtype=torch.bfloat16)
         fn = lambda: flash.flash_fwd(qkv, 8, 4096, 32, 8, 128)
         work = 4.0 * 8 * 32 * 4096 * 4096 * 128 / 2
+    elif kind == "flashbwd":  # causal attention backward, 4 x 4096 tokens, 32 query / 8 KV heads of 128
+        from aicomp_b200.ops import flash
+        B, S = 4, 4096
+        qkv = torch.randn(B * S, (32 + 16) * 128, device=dev, dtype=torch.bfloat16)
+        dout = torch.randn(B * S, 32 * 128, device=dev, dtype=torch.bfloat16)
+        out, lse = flash.flash_fwd(qkv, B, S, 32, 8, 128, need_lse=True)
+        fn = lambda: flash.flash_bwd(qkv, out, dout, lse, B, S, 32, 8, 128)
+        work = 2.5 * 4.0 * B * 32 * S * S * 128 / 2
     elif kind == "rmsnorm":  # 65536 x 4096 bf16: 512 MB in, 512 MB out
         x = torch.randn(65536, 4096, device=dev, dtype=torch.bfloat16)
         w = torch.ones(4096, device=dev, dtype=torch.bfloat16)
@@ -108,6 +148,8 @@ if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     if what == "gemm":
         bench_gemm()
+    elif what == "attention":
+        bench_attention()
     elif what == "small":
         small_case(sys.argv[2] if len(sys.argv) > 2 else "gemm")
     else:
