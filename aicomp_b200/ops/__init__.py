@@ -8,6 +8,7 @@ same math, which is also the oracle the GPU tests compare against.
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -24,6 +25,9 @@ __all__ = [
 GEMM_OUT_F32 = 1
 GEMM_ACCUMULATE = 2
 GEMM_BIAS = 4
+
+# Large GEMMs run on CTA pairs (two SMs per 256 x 256 tile); AICOMP_PAIR_GEMM=0 keeps every GEMM on the single-CTA kernel.
+PAIR_GEMM = os.environ.get("AICOMP_PAIR_GEMM", "1") != "0"
 
 _launches = 0
 
@@ -70,8 +74,11 @@ def _rows(t: torch.Tensor) -> torch.Tensor:
 # ---------------------------------------------------------------------- GEMM
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: Optional[torch.Tensor] = None,
          out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False, bias: Optional[torch.Tensor] = None,
-         alpha: float = 1.0, bn: int = 0, max_ctas: int = 0, ksplit: int = 1) -> torch.Tensor:
+         alpha: float = 1.0, bn: int = 0, max_ctas: int = 0, ksplit: int = 1, pair: Optional[bool] = None) -> torch.Tensor:
     """``C[M,N] (+)= alpha * A @ B^T (+ bias)`` on tcgen05 tensor cores.
+
+    ``pair``: run the CTA-pair kernel (``cta_group::2``, 256 x 256 tiles); default: whenever the problem is large
+    enough for it (``PAIR_GEMM`` switches the default off).
 
     ``a`` is ``[M,K]`` (or ``[K,M]`` when ``a_mn``), ``b`` is ``[N,K]`` (or
     ``[K,N]`` when ``b_mn``): the ``*_mn`` forms read a transposed operand in
@@ -109,9 +116,16 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if bias is not None and (bias.dtype != torch.bfloat16 or not bias.is_contiguous()):
         bias = bias.to(torch.bfloat16).contiguous()
     lib = _lib.require()
-    rc = lib.b200_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(bias), M, N, K,
-                            a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn), flags, float(alpha),
-                            bn, max_ctas, ksplit, _lib.err_word(a.device).data_ptr(), _lib.stream_ptr())
+    if pair is None:
+        pair = PAIR_GEMM and bn == 0 and ksplit == 1
+    if pair and ksplit == 1 and hasattr(lib, "b200_gemm2_bf16") and lib.b200_gemm2_supported(M, N, K):
+        rc = lib.b200_gemm2_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(bias), M, N, K,
+                                 a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn), flags, float(alpha),
+                                 max_ctas, _lib.err_word(a.device).data_ptr(), _lib.stream_ptr())
+    else:
+        rc = lib.b200_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(bias), M, N, K,
+                                a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn), flags, float(alpha),
+                                bn, max_ctas, ksplit, _lib.err_word(a.device).data_ptr(), _lib.stream_ptr())
     _lib.check_rc(rc, "gemm")
     _count()
     return out

@@ -28,6 +28,8 @@ F = c_float
 
 _PROTOS = {
     "b200_gemm_bf16": [P, P, P, P, I, I, I, L, L, L, I, I, I, F, I, I, I, P, P],
+    "b200_gemm2_bf16": [P, P, P, P, I, I, I, L, L, L, I, I, I, F, I, P, P],
+    "b200_gemm2_supported": [I, I, I],
     "b200_norm_bwd_ctas": [],
     "b200_norm_fwd": [P, P, P, P, P, P, P, P, I, I, F, I, P],
     "b200_norm_bwd": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P],

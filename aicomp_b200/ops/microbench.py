@@ -44,6 +44,7 @@ def bench_gemm(shapes=None):
         (2048, 4096, 28672, False, True, False, "gate_up dgrad"),
         (28672, 4096, 2048, True, True, True, "gate_up wgrad"),
         (4096, 14336, 2048, True, True, True, "down wgrad"),
+        (6144, 4096, 2048, True, True, True, "qkv wgrad"),
         (8192, 8192, 8192, False, False, False, "square 8k"),
         (2048, 128256, 4096, False, False, False, "lm_head fwd"),
     ]
@@ -57,6 +58,9 @@ def bench_gemm(shapes=None):
             t = _time(lambda: ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, accumulate=acc, bn=bn), flush=flush)
             res[f"ours_bn{bn}_ms"] = round(t, 4)
             res[f"ours_bn{bn}_tflops"] = round(flops / t / 1e9, 1)
+        t = _time(lambda: ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, accumulate=acc, pair=True), flush=flush)
+        res["ours_pair_ms"] = round(t, 4)
+        res["ours_pair_tflops"] = round(flops / t / 1e9, 1)
         A = a.t() if a_mn else a
         B = b if b_mn else b.t()
         if acc:  # cuBLAS has no bf16-in / fp32-accumulate-into form through torch: time the plain bf16 product

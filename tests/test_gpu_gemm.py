@@ -95,3 +95,45 @@ def test_small_m_linear_split_k(M, N, K):
     ops.gemm(x, w, out=acc, accumulate=True, ksplit=7, bn=128)
     assert torch.allclose(acc, x.float() @ w.float().t(), rtol=1e-3, atol=2e-2)
     ops.check_errors()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(512, 256, 64), (512, 512, 448), (2048, 6144, 4096), (4096, 4096, 2048), (1000, 520, 264),
+                                   (640, 1032, 128)])
+def test_pair_gemm_layouts(a_mn, b_mn, M, N, K):
+    """CTA-pair kernel (cta_group::2, 256 x 256 tiles, each CTA stages half of B) vs fp32 PyTorch."""
+    torch.manual_seed(0)
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda", dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda", dtype=torch.bfloat16)
+    c = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, pair=True)
+    torch.cuda.synchronize()
+    ops.check_errors()
+    ref = _ref(a, b, a_mn, b_mn)
+    err = (c.float() - ref).abs().max().item()
+    scale = ref.abs().max().item()
+    assert err <= 1e-2 * scale + 1e-2, f"max err {err} (scale {scale})"
+
+
+def test_pair_gemm_fp32_accumulate_bias_and_repeat():
+    torch.manual_seed(1)
+    M, N, K = 1024, 768, 320
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    acc = torch.randn(M, N, device="cuda", dtype=torch.float32)
+    acc0 = acc.clone()
+    for _ in range(3):
+        ops.gemm(a, b, out=acc, accumulate=True, pair=True)
+    torch.cuda.synchronize()
+    ref = acc0 + 3 * (a.float() @ b.float().t())
+    assert torch.allclose(acc, ref, rtol=1e-3, atol=2e-2)
+    c = ops.gemm(a, b, bias=bias, alpha=0.5, pair=True)
+    ref2 = 0.5 * (a.float() @ b.float().t()) + bias.float()
+    assert (c.float() - ref2).abs().max().item() <= 1e-2 * ref2.abs().max().item()
+    # many tiles per pair: exercises the ring wrap-around and both accumulator buffers
+    a2 = torch.randn(8192, 512, device="cuda", dtype=torch.bfloat16)
+    b2 = torch.randn(8192, 512, device="cuda", dtype=torch.bfloat16)
+    c2 = ops.gemm(a2, b2, pair=True)
+    ref3 = a2.float() @ b2.float().t()
+    assert (c2.float() - ref3).abs().max().item() <= 1e-2 * ref3.abs().max().item()
+    ops.check_errors()
