@@ -109,17 +109,18 @@ def bench_attention(shapes=None):
 def small_case(kind: str, launches: int = 3) -> None:
     """A few launches of one kernel on inputs larger than L2 and well under 2 GB: the case a profiler captures."""
     dev = "cuda"
-    if kind == "gemm":      # gate_up forward of Llama-3-8B on 8192 tokens: A 64 MB, B 224 MB, C 448 MB
+    if kind in ("gemm", "gemm1"):  # gate_up forward of Llama-3-8B on 8192 tokens: A 64 MB, B 224 MB, C 448 MB
         a = torch.randn(8192, 4096, device=dev, dtype=torch.bfloat16)
         b = torch.randn(28672, 4096, device=dev, dtype=torch.bfloat16)
         out = torch.empty(8192, 28672, device=dev, dtype=torch.bfloat16)
-        fn = lambda: ops.gemm(a, b, out=out, bn=256)
+        # "gemm": the CTA-pair kernel (default for this size); "gemm1": the single-CTA kernel with 128 x 256 tiles
+        fn = (lambda: ops.gemm(a, b, out=out)) if kind == "gemm" else (lambda: ops.gemm(a, b, out=out, bn=256))
         work = 2.0 * 8192 * 28672 * 4096
     elif kind == "wgrad":   # gate_up weight gradient, fp32 accumulate in memory (TMA reduce-add epilogue)
         x = torch.randn(8192, 4096, device=dev, dtype=torch.bfloat16)
         dy = torch.randn(8192, 28672, device=dev, dtype=torch.bfloat16)
         out = torch.zeros(28672, 4096, device=dev, dtype=torch.float32)
-        fn = lambda: ops.gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=True, bn=256)
+        fn = lambda: ops.gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=True)
         work = 2.0 * 8192 * 28672 * 4096
     elif kind == "flash":   # causal attention forward on packed QKV: 8 x 4096 tokens, 32 query / 8 KV heads of 128
         from aicomp_b200.ops import flash
