@@ -30,7 +30,16 @@ def _path(engine, step: int, epoch: int) -> str:
 def save_ckpt(engine, step: int, epoch: int, keep: int = 2) -> Optional[str]:
     if not engine.checkpoint:
         raise RuntimeError("construct the engine with checkpoint=True to save checkpoints")
+    sharded_opt = engine.optimizer is not None and getattr(engine.optimizer, "_dp_group", None) is not None
     if engine.tpl.dp_rank != 0:
+        if sharded_opt:  # every data-parallel rank owns a slice of the optimizer state
+            if engine.use_gpu:
+                torch.cuda.synchronize()
+            os.makedirs(engine.ckpt_dir, exist_ok=True)
+            shard_path = _path(engine, step, epoch) + f".optdp{engine.tpl.dp_rank}"
+            torch.save({"optimizer_state_dict": _cpu_tree(engine.optimizer.state_dict())}, shard_path + ".tmp")
+            os.replace(shard_path + ".tmp", shard_path)
+            return shard_path
         return None
     if engine.use_gpu:
         torch.cuda.synchronize()
@@ -90,8 +99,11 @@ def load_ckpt(engine, step: int, epoch: int) -> dict:
     if state.get("stage", engine.tpl.stage) != engine.tpl.stage:
         raise ValueError(f"checkpoint is for stage {state['stage']}, this rank runs stage {engine.tpl.stage}")
     engine.stage_module.load_state_dict(state["stage_state_dict"])
-    if engine.optimizer is not None and state.get("optimizer_state_dict") is not None:
-        engine.optimizer.load_state_dict(state["optimizer_state_dict"])
+    opt_state = state.get("optimizer_state_dict")
+    if engine.optimizer is not None and getattr(engine.optimizer, "_dp_group", None) is not None and engine.tpl.dp_rank != 0:
+        opt_state = torch.load(path + f".optdp{engine.tpl.dp_rank}", map_location="cpu", weights_only=False)["optimizer_state_dict"]
+    if engine.optimizer is not None and opt_state is not None:
+        engine.optimizer.load_state_dict(opt_state)
     if state.get("rng_state") is not None:
         torch.set_rng_state(state["rng_state"])
     if engine.use_gpu and state.get("cuda_rng_state") is not None:

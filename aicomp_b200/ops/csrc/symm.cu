@@ -230,6 +230,27 @@ extern "C" int b200_allreduce_mean_f32(void* const* buf_ptrs, void* const* flag_
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
+// Reduce-scatter only (sharded optimizer): afterwards rank r holds the mean over all ranks in its own slice
+// [r*chunk, (r+1)*chunk), chunk = ceil(n/4/world)*4 elements; the rest of its buffer still holds its local values.
+// Returns after every peer has finished reading this rank's buffer, so the caller may overwrite it.
+extern "C" int b200_reduce_scatter_mean_f32(void* const* buf_ptrs, void* const* flag_ptrs, int rank, int world, long long n,
+                                            int slot, unsigned int epoch, int ctas, int* err, cudaStream_t stream) {
+  if (world > MAX_PEERS || n % 4) return -10;
+  if (n <= 0) return 0;
+  const long long n4 = n / 4;
+  const long long chunk4 = (n4 + world - 1) / world;
+  if (ctas <= 0) ctas = 148 * 2;
+  long long need = (chunk4 + 511) / 512;
+  if (need < ctas) ctas = static_cast<int>(need < 1 ? 1 : need);
+  PeerPtrs bufs = to_peers(buf_ptrs, world), flags = to_peers(flag_ptrs, world);
+  const uint32_t* mine = static_cast<const uint32_t*>(flag_ptrs[rank]);
+  signal_kernel<<<1, 32, 0, stream>>>(flags, rank, world, slot, epoch);                    // my gradients are final
+  reduce_scatter_mean_kernel<<<ctas, 512, 0, stream>>>(bufs, mine, rank, world, slot, epoch, chunk4, n4, 1.0f / world, err);
+  signal_kernel<<<1, 32, 0, stream>>>(flags, rank, world, slot + 2, epoch);                // I no longer read peers
+  wait_kernel<<<1, 32, 0, stream>>>(mine, world, slot + 2, epoch, err);                    // nobody reads me any more
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
 extern "C" int b200_peer_pull(void* dst, const void* src, long long bytes, int ctas, cudaStream_t stream) {
   if (bytes % 16) return -10;
   if (bytes <= 0) return 0;

@@ -84,6 +84,9 @@ class FusedAdamW(torch.optim.Optimizer):
             p.grad_accumulated = False
         self._norm_sq = torch.zeros(2, dtype=torch.float32, device=dev)
         self.total = total
+        # data-parallel sharding of the optimizer state (set by attach_to_reducer): this rank updates [lo, hi) only
+        self.shard = (0, total)
+        self._dp_group = None
 
     # ------------------------------------------------------------------ gradient plumbing
     def _fold_param_grads(self) -> None:
@@ -101,18 +104,58 @@ class FusedAdamW(torch.optim.Optimizer):
                 dst.add_(g.reshape(-1).float())
             p.grad = None
 
-    def attach_to_reducer(self, reducer) -> None:
-        """Let a data-parallel ``GradReducer`` reduce the contiguous gradient arena in place."""
-        if self.fused and reducer is not None:
-            fused = getattr(reducer, "_fused", None)
-            if fused is not None:  # move the gradient arena into peer-mapped memory (collective over the DP group)
-                new = fused.alloc_arena(self.total)
-                new.copy_(self.grad)
-                self.grad = new
-                for p, o in zip(self._order, self.offsets):
-                    p.main_grad = self.grad[o:o + p.numel()].view(p.shape)
-            reducer.arena_grad = self.grad
-            reducer.pre_reduce = self._fold_param_grads
+    def attach_to_reducer(self, reducer, shard_state: bool = True) -> None:
+        """Let a data-parallel ``GradReducer`` reduce the contiguous gradient arena in place.
+
+        ``shard_state`` (default): the optimizer state is sharded over the data-parallel group.  The reducer then only
+        reduce-scatters the gradient arena, every rank keeps master weights and moments for its own 1/dp slice, updates
+        that slice, and the bf16 weights are all-gathered after the update.  Per step this moves 3/4 of the bytes of
+        an all-reduce of the fp32 gradients and runs the update kernel over 1/dp of the parameters.
+        """
+        if not (self.fused and reducer is not None):
+            return
+        dp = reducer.dp_size
+        shard = bool(shard_state) and dp > 1 and self._step == 0
+        if shard and self.total % (8 * dp):   # equal 16-byte aligned slices for the all-gather of the weights
+            self._repad(((self.total + 8 * dp - 1) // (8 * dp)) * 8 * dp)
+        fused = getattr(reducer, "_fused", None)
+        if fused is not None:  # move the gradient arena into peer-mapped memory (collective over the DP group)
+            new = fused.alloc_arena(self.total)
+            new.copy_(self.grad)
+            self.grad = new
+            for p, o in zip(self._order, self.offsets):
+                p.main_grad = self.grad[o:o + p.numel()].view(p.shape)
+        reducer.arena_grad = self.grad
+        reducer.pre_reduce = self._fold_param_grads
+        if shard:
+            lo, hi = reducer.shard_bounds(self.total)
+            self.shard = (lo, hi)
+            self._dp_group = reducer.group
+            self.master = self.p16[lo:hi].float()
+            self.m = torch.zeros(hi - lo, dtype=torch.float32, device=self.p16.device)
+            self.v = torch.zeros(hi - lo, dtype=torch.float32, device=self.p16.device)
+            reducer.arena_mode = "reduce_scatter"
+
+    def _repad(self, new_total: int) -> None:
+        """Grow the flat buffers to ``new_total`` elements (tail padding), keeping every parameter where it is."""
+        dev = self.p16.device
+        p16 = torch.zeros(new_total, dtype=torch.bfloat16, device=dev)
+        p16[:self.total].copy_(self.p16)
+        self.p16 = p16
+        grad = torch.zeros(new_total, dtype=torch.float32, device=dev)
+        grad[:self.total].copy_(self.grad)
+        self.grad = grad
+        for p, o in zip(self._order, self.offsets):
+            p.data = self.p16[o:o + p.numel()].view(p.shape)
+            p.main_grad = self.grad[o:o + p.numel()].view(p.shape)
+        self.master = self.p16.float()
+        self.m = torch.zeros(new_total, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(new_total, dtype=torch.float32, device=dev)
+        if self._group_ranges:
+            lo, _ = self._group_ranges[-1]
+            self._group_ranges[-1] = (lo, new_total)
+        self.total = new_total
+        self.shard = (0, new_total)
 
     def grad_norm(self) -> torch.Tensor:
         """Global L2 norm of the (unscaled) gradient; reduces over the ``tp`` / ``pp`` groups given in ``norm_groups``."""
@@ -126,10 +169,15 @@ class FusedAdamW(torch.optim.Optimizer):
         lib = _lib.require()
         self._norm_sq.zero_()
         se = self._sharded_end
-        if se:
-            _lib.check_rc(lib.b200_sumsq(self.grad.data_ptr(), se, self._norm_sq[0:1].data_ptr(), _lib.stream_ptr()), "sumsq")
-        if self.total - se:
-            _lib.check_rc(lib.b200_sumsq(self.grad[se:].data_ptr(), self.total - se, self._norm_sq[1:2].data_ptr(), _lib.stream_ptr()), "sumsq")
+        lo, hi = self.shard   # with a sharded optimizer only this rank's slice holds reduced gradients
+        a0, a1 = lo, min(hi, se)
+        if a1 > a0:
+            _lib.check_rc(lib.b200_sumsq(self.grad[a0:].data_ptr(), a1 - a0, self._norm_sq[0:1].data_ptr(), _lib.stream_ptr()), "sumsq")
+        b0, b1 = max(lo, se), hi
+        if b1 > b0:
+            _lib.check_rc(lib.b200_sumsq(self.grad[b0:].data_ptr(), b1 - b0, self._norm_sq[1:2].data_ptr(), _lib.stream_ptr()), "sumsq")
+        if self._dp_group is not None:
+            dist.all_reduce(self._norm_sq, group=self._dp_group)
         tp, pp = self.norm_groups.get("tp"), self.norm_groups.get("pp")
         if tp is not None:
             dist.all_reduce(self._norm_sq[0:1], group=tp)
@@ -152,16 +200,26 @@ class FusedAdamW(torch.optim.Optimizer):
         if self.max_grad_norm > 0:
             self._norm_total = self._compute_norm_sq()  # kept alive until the update kernel has read it
             norm_ptr = self._norm_total.data_ptr()
-        for g, (lo, hi) in zip(self.param_groups, self._group_ranges):
+        s_lo, s_hi = self.shard
+        for g, (g_lo, g_hi) in zip(self.param_groups, self._group_ranges):
+            lo, hi = max(g_lo, s_lo), min(g_hi, s_hi)
             if hi <= lo:
                 continue
             b1, b2 = g["betas"]
-            rc = lib.b200_adamw(self.p16[lo:].data_ptr(), self.master[lo:].data_ptr(), self.m[lo:].data_ptr(), self.v[lo:].data_ptr(),
+            so = lo - s_lo   # master weights and moments exist for this rank's slice only
+            rc = lib.b200_adamw(self.p16[lo:].data_ptr(), self.master[so:].data_ptr(), self.m[so:].data_ptr(), self.v[so:].data_ptr(),
                                 self.grad[lo:].data_ptr(), None, norm_ptr, hi - lo, float(g["lr"]), float(b1), float(b2),
                                 float(g["eps"]), float(g["weight_decay"]), self._step, self.grad_scale, self.max_grad_norm, 1,
                                 _lib.stream_ptr())
             _lib.check_rc(rc, "adamw")
             ops._count()
+        if self._dp_group is not None:
+            # the update kernel cleared the gradient of this slice; the other slices hold this rank's unreduced values
+            if s_lo > 0:
+                self.grad[:s_lo].zero_()
+            if s_hi < self.total:
+                self.grad[s_hi:].zero_()
+            dist.all_gather_into_tensor(self.p16, self.p16[s_lo:s_hi], group=self._dp_group)
         self._grad_is_zero = True
         for p in self._order:
             p.grad_accumulated = False
@@ -185,7 +243,7 @@ class FusedAdamW(torch.optim.Optimizer):
     def state_dict(self):
         if not self.fused:
             return self._fallback.state_dict()
-        return {"fused": True, "step": self._step, "master": self.master, "m": self.m, "v": self.v,
+        return {"fused": True, "step": self._step, "master": self.master, "m": self.m, "v": self.v, "shard": tuple(self.shard),
                 "shapes": [tuple(p.shape) for p in self._order], "offsets": list(self.offsets),
                 "param_groups": [{k: v for k, v in g.items() if k != "params"} for g in self.param_groups]}
 
@@ -194,6 +252,8 @@ class FusedAdamW(torch.optim.Optimizer):
             return self._fallback.load_state_dict(sd)
         if [tuple(s) for s in sd["shapes"]] != [tuple(p.shape) for p in self._order]:
             raise ValueError("optimizer state was saved for a different parameter layout")
+        if tuple(sd.get("shard", (0, self.total))) != tuple(self.shard):
+            raise ValueError("optimizer state was saved with a different data-parallel sharding")
         self._step = int(sd["step"])
         self.master.copy_(sd["master"])
         self.m.copy_(sd["m"])

@@ -57,6 +57,21 @@ class GradReducer:
         if pre is not None:
             pre()
         arena = getattr(self, "arena_grad", None)
+        if arena is not None and getattr(self, "arena_mode", "all_reduce") == "reduce_scatter":
+            # sharded optimizer: every rank needs the mean of its own slice only
+            self.bytes_reduced += arena.numel() * arena.element_size()
+            if self._fused is not None and self._fused.supports(arena):
+                self._fused.reduce_scatter_mean_(arena)
+            else:
+                lo, hi = self.shard_bounds(arena.numel())
+                chunk = ((arena.numel() // 4 + self.dp_size - 1) // self.dp_size) * 4
+                if chunk * self.dp_size == arena.numel():
+                    dist.reduce_scatter_tensor(arena[lo:hi], arena, group=self.group)
+                    arena[lo:hi].div_(self.dp_size)
+                else:
+                    dist.all_reduce(arena, group=self.group)
+                    arena.div_(self.dp_size)
+            return
         if arena is not None:  # contiguous fp32 gradient arena (FusedAdamW): reduce it in place, bucket by bucket
             n = arena.numel()
             step = BUCKET_BYTES // arena.element_size()
@@ -77,6 +92,13 @@ class GradReducer:
             size += nbytes
         if bucket:
             self._reduce_bucket(bucket)
+
+    def shard_bounds(self, numel: int):
+        """Slice [lo, hi) of a flat ``numel``-element arena owned by this rank of the data-parallel group."""
+        rank = dist.get_rank(self.group)
+        chunk = ((numel // 4 + self.dp_size - 1) // self.dp_size) * 4
+        lo = min(rank * chunk, numel)
+        return lo, min(lo + chunk, numel)
 
     def _reduce_flat(self, flat: torch.Tensor) -> None:
         self.bytes_reduced += flat.numel() * flat.element_size()

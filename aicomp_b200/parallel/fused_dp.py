@@ -52,3 +52,19 @@ class FusedGradAllReduce:
                                          self.SLOT, epoch, 0, _lib.err_word(self.device).data_ptr(), _lib.stream_ptr())
         _lib.check_rc(rc, "allreduce_mean_f32")
         ops._count(6)
+
+    def shard_bounds(self, numel: int):
+        """Slice of an ``numel``-element region that this rank owns after :meth:`reduce_scatter_mean_`."""
+        chunk = ((numel // 4 + self.dp_size - 1) // self.dp_size) * 4
+        lo = min(self.rank * chunk, numel)
+        return lo, min(lo + chunk, numel)
+
+    def reduce_scatter_mean_(self, flat: torch.Tensor) -> None:
+        """In place: this rank's slice of ``flat`` becomes the mean over the group (the other slices keep local values)."""
+        lib = _lib.require()
+        off = flat.data_ptr() - self._base
+        epoch = self.flags.next_epoch(self.SLOT, span=3)
+        rc = lib.b200_reduce_scatter_mean_f32(self.arena.ptr_array(off), self.flags._ptrs, self.rank, self.dp_size, flat.numel(),
+                                              self.SLOT, epoch, 0, _lib.err_word(self.device).data_ptr(), _lib.stream_ptr())
+        _lib.check_rc(rc, "reduce_scatter_mean_f32")
+        ops._count(4)

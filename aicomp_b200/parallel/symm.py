@@ -28,6 +28,8 @@ _lib.OPTIONAL_PROTOS.update({
     "b200_wait": [P, ctypes.c_int, ctypes.c_int, ctypes.c_uint, P, P],
     "b200_allreduce_mean_f32": [ctypes.POINTER(P), ctypes.POINTER(P), ctypes.c_int, ctypes.c_int, ctypes.c_longlong, ctypes.c_int,
                                 ctypes.c_uint, ctypes.c_int, P, P],
+    "b200_reduce_scatter_mean_f32": [ctypes.POINTER(P), ctypes.POINTER(P), ctypes.c_int, ctypes.c_int, ctypes.c_longlong, ctypes.c_int,
+                                     ctypes.c_uint, ctypes.c_int, P, P],
     "b200_peer_pull": [P, P, ctypes.c_longlong, ctypes.c_int, P],
     "b200_kv_push": [P, P, P, P, ctypes.c_int, ctypes.c_int, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_int, P, ctypes.c_uint,
                      P, P],

@@ -70,3 +70,20 @@ def test_pp2_peer_transport_and_graph_replay_match_nccl_eager():
         got = [r["losses"] for r in res if r["losses"][0] is not None][0]
         for x, y in zip(want, got):
             assert abs(x - y) < 2e-2 * abs(x), (name, want, got)
+
+
+def test_dp2_sharded_optimizer_matches_replicated():
+    """FusedAdamW with its state sharded over the DP group (reduce-scatter + update of a slice + all-gather of the
+    weights) follows the replicated optimizer (all-reduce + full update), and the replicas stay identical."""
+    _need(2)
+    base = {"model": "llama_d128", "pp": 1, "dp": 2, "num_mb": 2, "steps": 5, "batch": 8, "use_gpu": True, "dtype": "bfloat16",
+            "seq": 256, "fused_adamw": True, "dp_backend": "fused"}
+    env = {"NCCL_NVLS_ENABLE": "0"}
+    rep = run_workers("train_worker", 2, dict(base, shard=False), timeout=300, env_extra=env)
+    shd = run_workers("train_worker", 2, dict(base, shard=True), timeout=300, env_extra=env)
+    nccl = run_workers("train_worker", 2, dict(base, shard=True, dp_backend="nccl"), timeout=300, env_extra=env)
+    for res in (shd, nccl):
+        assert abs(res[0]["checksum"] - res[1]["checksum"]) <= 1e-6 * abs(res[0]["checksum"]), "replicas diverged"
+        for x, y in zip(rep[0]["losses"], res[0]["losses"]):
+            assert abs(x - y) < 2e-2 * abs(x), (rep[0]["losses"], res[0]["losses"])
+    assert rep[0]["losses"][-1] < rep[0]["losses"][0]

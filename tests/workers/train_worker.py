@@ -23,7 +23,14 @@ def main():
                   ir_analyze=__import__("aicomp_b200").IR_Anal[a.get("ir", "PARALLEL")], dynamo_capture=a.get("dynamo", False),
                   fused_kernels=False if a.get("dynamo") else None, cuda_graphs=a.get("graphs", False),
                   pp_backend=a.get("pp_backend", "auto"))
-    opt = torch.optim.AdamW(e.parameters(), lr=a.get("lr", 1e-3))
+    if a.get("fused_adamw"):
+        from aicomp_b200 import FusedAdamW
+        opt = FusedAdamW(e.parameters(), lr=a.get("lr", 1e-3), grad_scale=1.0 / a.get("num_mb", 2), max_grad_norm=1.0,
+                         norm_groups={"pp": e.tpl.pp_group} if e.tpl.pp_size > 1 else None)
+        if e.dp is not None:
+            opt.attach_to_reducer(e.dp, shard_state=a.get("shard", True))
+    else:
+        opt = torch.optim.AdamW(e.parameters(), lr=a.get("lr", 1e-3))
     e.optimizer = opt
     losses = []
     for step in range(a.get("steps", 3)):
