@@ -36,6 +36,9 @@ def parse():
     ap.add_argument("--dp-backend", default="fused")
     ap.add_argument("--attn", default="auto")
     ap.add_argument("--no-graphs", action="store_true", help="issue every kernel from Python instead of replaying CUDA graphs")
+    ap.add_argument("--layout", default="", help="pp,dp,tp override, e.g. 2,1,4 with --seq 4096 --seqs-per-gpu 4 for the "
+                                                 "TP4 x PP2 config (the metric line then names that parallelism)")
+    ap.add_argument("--tp-backend", default="fused")
     return ap.parse_args()
 
 
@@ -96,6 +99,11 @@ def run_ours(a):
     if world != a.gpus:
         raise SystemExit(f"--gpus {a.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {a.gpus}")
     pp, dp = layout_for(a.gpus)
+    tp = 1
+    if a.layout:
+        pp, dp, tp = (int(v) for v in a.layout.split(","))
+        if pp * dp * tp != a.gpus:
+            raise SystemExit(f"--layout {a.layout} does not use {a.gpus} GPUs")
     cfg = LlamaConfig(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=a.layers,
                       num_attention_heads=32, num_key_value_heads=8, rms_norm_eps=1e-5, max_position_embeddings=8192,
                       rope_theta=500000.0, tie_word_embeddings=False, attention_bias=False)
@@ -103,11 +111,11 @@ def run_ours(a):
         model = LlamaForCausalLM(cfg)
     seqs_per_replica = a.seqs_per_gpu * a.gpus // dp
     num_mb = seqs_per_replica  # micro-batch 1
-    eng = Optimus_p(model, num_mb=num_mb, use_gpu=True, pp_size=pp, dp_size=dp, tp_size=1, dtype=torch.bfloat16,
-                    dp_backend=a.dp_backend, cuda_graphs=not a.no_graphs)
+    eng = Optimus_p(model, num_mb=num_mb, use_gpu=True, pp_size=pp, dp_size=dp, tp_size=tp, dtype=torch.bfloat16,
+                    dp_backend=a.dp_backend, tp_backend=a.tp_backend, cuda_graphs=not a.no_graphs)
     dev = eng.device
     opt = FusedAdamW(eng.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1, grad_scale=1.0 / num_mb, max_grad_norm=1.0,
-                     norm_groups={"pp": eng.tpl.pp_group})
+                     norm_groups={"pp": eng.tpl.pp_group, "tp": eng.tpl.tp_group if tp > 1 else None})
     eng.optimizer = opt
     if eng.dp is not None:
         opt.attach_to_reducer(eng.dp)
@@ -179,7 +187,7 @@ def run_ours(a):
             "impl": "ours",
             "config": {"model": "Llama-3-8B" if a.layers == 32 else f"Llama-3-8B-width/{a.layers}L (INVALID: reduced)",
                        "global_batch": gbs, "seq_len": S, "micro_batch": 1, "num_microbatches": num_mb,
-                       "parallelism": f"pp{pp}xdp{dp}", "schedule": "1f1b", "optimizer": "AdamW fp32 master + bf16 weights",
+                       "parallelism": f"pp{pp}xdp{dp}" + (f"xtp{tp}" if tp > 1 else ""), "schedule": "1f1b", "optimizer": "AdamW fp32 master + bf16 weights",
                        "l2": "inputs larger than L2: every step streams >100 GB of weights, gradients and optimizer state"},
             "clocks": clocks,
             "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(2 * gbs * S * 8), "d2h_bytes_per_step": 4,
