@@ -42,7 +42,7 @@ def main(argv=None):
     per_replica = a.gbs // a.dp
     num_mb = per_replica // a.mbs
     eng = Optimus_p(model, num_mb=num_mb, use_gpu=True, pp_size=a.pp, dp_size=a.dp, tp_size=a.tp, dtype=torch.bfloat16,
-                    tp_backend=a.tp_backend, dp_backend=a.dp_backend)
+                    tp_backend=a.tp_backend, dp_backend=a.dp_backend, cuda_graphs=True)
     opt = FusedAdamW(eng.parameters(), lr=1e-4, grad_scale=1.0 / num_mb, max_grad_norm=1.0,
                      norm_groups={"pp": eng.tpl.pp_group, "tp": eng.tpl.tp_group})
     if eng.dp is not None:

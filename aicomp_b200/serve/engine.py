@@ -30,10 +30,11 @@ class ServingEngine:
     def __init__(self, module: nn.Module, tp_size: int = 1, use_gpu: bool = True, dtype: torch.dtype = torch.bfloat16,
                  num_pages: Optional[int] = None, max_seqs: int = 256, max_seq_len: int = 4096, cuda_graphs: bool = True,
                  kv_memory_fraction: float = 0.85, pool: Optional[torch.Tensor] = None, tp_backend: str = "nccl",
-                 max_prefill_per_step: int = 4):
+                 max_prefill_per_step: int = 4, dp_size: int = 1):
         if not torch.cuda.is_available() or not use_gpu:
             dtype, cuda_graphs = (torch.float32 if dtype == torch.bfloat16 else dtype), False
-        self._e = Optimus_p(module, num_mb=1, use_gpu=use_gpu, pp_size=1, dp_size=1, tp_size=tp_size, dtype=dtype,
+        # dp_size > 1: independent replicas inside one job (weights are broadcast from the first replica at set-up)
+        self._e = Optimus_p(module, num_mb=1, use_gpu=use_gpu, pp_size=1, dp_size=dp_size, tp_size=tp_size, dtype=dtype,
                             sequence_parallel=False, tp_backend=tp_backend, input_names=["input_ids", "position_ids"],
                             trace_kwargs={"logits_to_keep": 1})
         self._e.eval()

@@ -45,3 +45,38 @@ def test_serving_engine_matches_hf_greedy():
     got = {r.rid: r.generated for r in eng.scheduler.finished}
     assert [got[i] for i in range(4)] == want
     assert m["requests"] == 4 and m["unfinished"] == 0 and eng.cache.alloc.available() == 63
+
+
+def test_pd_disaggregated_protocol_matches_hf_greedy():
+    """Prefill worker + decode worker over the loopback transport: pages prefilled in one cache and pushed into the
+    other give the tokens of plain greedy decoding, with back-pressure on the decode pool."""
+    from aicomp_b200.serve.engine import ServingEngine
+    from aicomp_b200.serve.pd_engine import DecodeWorker, LoopbackTransport, PrefillWorker
+    from aicomp_b200.serve.scheduler import Request
+    ref = build_model("llama").eval()
+    prompts = [[5, 7, 11, 13, 17], [2, 3], [9] * 19, [1, 2, 3, 4, 5, 6, 7], [4] * 33]
+    news = [6, 9, 4, 12, 3]
+    want = []
+    for p, n in zip(prompts, news):
+        out = torch.tensor([p])
+        with torch.no_grad():
+            for _ in range(n):
+                out = torch.cat([out, ref(input_ids=out, use_cache=False).logits[:, -1].argmax(-1, keepdim=True)], 1)
+        want.append(out[0, len(p):].tolist())
+    pre = ServingEngine(build_model("llama"), use_gpu=False, num_pages=16, max_seqs=2, max_seq_len=64)
+    dec = ServingEngine(build_model("llama"), use_gpu=False, num_pages=7, max_seqs=3, max_seq_len=64)  # 6 usable pages: back-pressure
+    tr = LoopbackTransport(pre.cache, dec.cache)
+    mk = lambda: [Request(rid=i, prompt=p, max_new_tokens=n, arrival_s=0.01 * i) for i, (p, n) in enumerate(zip(prompts, news))]
+    pw, dw = PrefillWorker(pre, tr, mk()), DecodeWorker(dec, tr, mk(), max_running=3)
+    now, guard = 0.0, 0
+    while (pw.has_work() or dw.has_work()) and guard < 10000:
+        dw.step(now)
+        pw.step(now)
+        now += 0.01
+        guard += 1
+    assert not pw.has_work() and not dw.has_work()
+    got = {r.rid: r.generated for r in dw.finished}
+    assert [got[i] for i in range(len(prompts))] == want
+    assert dec.cache.alloc.available() == 6 and pre.cache.alloc.available() == 15
+    assert all(r.t_first_token is not None and r.t_finished >= r.t_first_token for r in dw.finished)
+    assert tr.bytes_pushed > 0
