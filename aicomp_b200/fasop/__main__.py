@@ -32,6 +32,8 @@ def parse(argv=None):
     ap.add_argument("--no-save-csv", action="store_true")
     ap.add_argument("--profile-dir", default=None)
     ap.add_argument("--top", type=int, default=10)
+    ap.add_argument("--placement", default="permutations", choices=["permutations", "cyclic", "grouped"],
+                    help="mixed clusters: which orders of the nodes along the pipeline to evaluate")
     return ap.parse_args(argv)
 
 
@@ -41,7 +43,7 @@ def main(argv=None):
         raise SystemExit("--gpus takes TYPE N pairs")
     gpus = [(a.gpus[i], int(a.gpus[i + 1])) for i in range(0, len(a.gpus), 2)]
     cfg = FasopConfig(gpus, a.model_type, a.dataset, a.gbs, a.gpu_per_node, a.precision, a.pp_partition_method, a.seq_len,
-                      verbose=a.verbose, profile_dir=a.profile_dir)
+                      verbose=a.verbose, profile_dir=a.profile_dir, pareto=a.pareto, placement=a.placement)
     if a.exhaustive:
         from .config import ModelConfig
         from .cost import estimate
@@ -62,7 +64,7 @@ def main(argv=None):
     print(f"{'rank':>4} {'gbs':>5} {'mbs':>4} {'tp':>3} {'dp':>3} {'pp':>3} {'step(s)':>9} {'samples/s':>10} {'mem(GB)':>8} oom partition")
     for r in results[:a.top]:
         print(f"{r.rank:>4} {r.gbs:>5} {r.mbs:>4} {r.tp:>3} {r.dp:>3} {r.pp:>3} {r.step_time:>9.4f} {r.throughput:>10.2f} "
-              f"{r.oom_gpumem:>8.1f} {str(r.is_oom):>5} {r.partition}")
+              f"{r.oom_gpumem:>8.1f} {str(r.is_oom):>5} {r.partition}" + (f" {r.node_type}" if "-" in r.node_type else ""))
     if not a.no_save_csv:
         save_csv(results, os.path.join("main_logs", exp + ".csv"))
     if a.pareto or a.make_pareto:

@@ -15,7 +15,7 @@ from typing import Dict, List, Optional, Tuple
 import numpy as np
 
 from .config import GPU_SPECS, LAYER_NODES, NODE_TYPES, ModelConfig
-from .partitioners import partition, stage_costs
+from .partitioners import partition, partition_hetero, stage_costs
 from .profiledb import ProfileDB
 from .sim1f1b import simulate
 
@@ -56,7 +56,17 @@ def allreduce_time(nbytes: float, n: int, spec: Dict[str, float], inter_node: bo
 
 def estimate(model: ModelConfig, db: ProfileDB, gpu: str, tp: int, dp: int, pp: int, mbs: int, gbs: int,
              method: str = "minmax", gpus_per_node: int = 8, precision_bytes: int = 2, schedule: str = "1f1b",
-             sequence_parallel: bool = True) -> Estimate:
+             sequence_parallel: bool = True, stage_gpus: Optional[List[str]] = None,
+             dbs: Optional[Dict[str, ProfileDB]] = None) -> Estimate:
+    """``stage_gpus`` (one GPU type per pipeline stage, with ``dbs`` holding a profile database per type) switches to
+    the heterogeneous model: every stage pays its own GPU's node costs, memory limit, all-reduce and optimizer
+    bandwidth, and a transfer between two stages runs at the slower side's link speed."""
+    if stage_gpus is not None and len(set(stage_gpus)) > 1:
+        return _estimate_hetero(model, dbs or {}, stage_gpus, tp, dp, pp, mbs, gbs, gpus_per_node, precision_bytes, schedule,
+                                sequence_parallel)
+    if stage_gpus:
+        gpu = stage_gpus[0]
+        db = (dbs or {}).get(gpu, db)
     spec = GPU_SPECS[gpu]
     if gbs % (dp * mbs):
         raise ValueError("gbs must be divisible by dp * mbs")
@@ -112,3 +122,66 @@ def estimate(model: ModelConfig, db: ProfileDB, gpu: str, tp: int, dp: int, pp: 
     layers = [(n - (1 if k == 0 else 0) - (1 if k == len(sizes) - 1 else 0)) / 8.0 for k, n in enumerate(sizes)]
     return Estimate(step, sf, sb, list(sizes), layers, pipe_time, max(dp_costs), tp_layer, max(opt_costs), mem, oom, num_mb, imb,
                     {"send_time": max(send) if send else 0.0})
+
+
+def _estimate_hetero(model: ModelConfig, dbs: Dict[str, ProfileDB], stage_gpus: List[str], tp: int, dp: int, pp: int, mbs: int,
+                     gbs: int, gpus_per_node: int, precision_bytes: int, schedule: str, sequence_parallel: bool) -> Estimate:
+    if len(stage_gpus) != pp:
+        raise ValueError("stage_gpus needs one GPU type per pipeline stage")
+    if gbs % (dp * mbs):
+        raise ValueError("gbs must be divisible by dp * mbs")
+    num_mb = gbs // (dp * mbs)
+    seq = model.node_sequence()
+    col = {n: i for i, n in enumerate(NODE_TYPES)}
+    tokens = mbs * model.seq_len
+    specs = [GPU_SPECS[g] for g in stage_gpus]
+    f_rows, b_rows = [], []
+    for g, spec in zip(stage_gpus, specs):
+        f_node, b_node = dbs[g].node_times(tp, mbs)
+        f = np.array([f_node[col[n]] for n in seq])
+        b = np.array([b_node[col[n]] for n in seq])
+        if tp > 1:
+            per_coll = spec["latency"] + (tp - 1) / tp * tokens * model.hidden * precision_bytes / spec["intra_p2p"]
+            extra = 4 * per_coll * (0.35 if g == "B200" else 1.0) / 2  # only B200 has the fused TP kernels
+            for i, n in enumerate(seq):
+                if n in ("attn_o", "mlp_down"):
+                    f[i] += extra
+                    b[i] += extra
+        f_rows.append(f)
+        b_rows.append(b)
+    world = tp * dp * pp
+    inter = world > gpus_per_node and (tp * dp) >= gpus_per_node
+    slow_link = min(specs, key=lambda sp: sp["inter_node"] if inter else sp["intra_p2p"])
+    cut_bytes = np.array([tokens * model.cut_elems(n, tp, sequence_parallel) * precision_bytes for n in seq])
+    comm = np.array([p2p_time(b, slow_link, inter) for b in cut_bytes])
+    sizes = partition_hetero([f + b for f, b in zip(f_rows, b_rows)], layer_level=(tp > 1), comm=comm)
+    sf, sb, stage_params, stage_act = [], [], [], []
+    i = 0
+    for s, n_nodes in enumerate(sizes):
+        sf.append(float(f_rows[s][i:i + n_nodes].sum()))
+        sb.append(float(b_rows[s][i:i + n_nodes].sum()))
+        nodes = seq[i:i + n_nodes]
+        stage_params.append(sum(model.node_params_sharded(n, tp) for n in nodes))
+        stage_act.append(sum(model.node_act_elems(n, tp) for n in nodes) * tokens * precision_bytes)
+        i += n_nodes
+    bounds = np.cumsum(sizes)[:-1]
+    send = []
+    for k, c in enumerate(bounds):  # the link between stage k and k+1 runs at the slower side's speed
+        pair = min((specs[k], specs[k + 1]), key=lambda sp: sp["inter_node"] if inter else sp["intra_p2p"])
+        send.append(p2p_time(float(cut_bytes[c - 1]), pair, inter))
+    ends, _ = simulate(sf, sb, send, send, num_mb, schedule)
+    dp_inter = dp * tp > gpus_per_node
+    dp_costs = [allreduce_time(p * 4, dp, sp, dp_inter, fused=(g == "B200")) for p, sp, g in zip(stage_params, specs, stage_gpus)]
+    opt_costs = [p * 30.0 / (0.8 * sp["hbm"]) for p, sp in zip(stage_params, specs)]
+    step = max(e + d + o for e, d, o in zip(ends, dp_costs, opt_costs))
+    mem, oom = [], False
+    for s, (p, a, sp) in enumerate(zip(stage_params, stage_act, specs)):
+        in_flight = min(num_mb, pp - s) if schedule == "1f1b" else num_mb
+        m = (p * BYTES_PARAM_STATE + a * in_flight) * 1.10 / 2**30 + 2.0
+        mem.append(m)
+        oom = oom or m > sp["mem_gb"]
+    sc = [a + b for a, b in zip(sf, sb)]
+    imb = (max(sc) - min(sc)) / max(sc) if max(sc) > 0 else 0.0
+    layers = [(n - (1 if k == 0 else 0) - (1 if k == len(sizes) - 1 else 0)) / 8.0 for k, n in enumerate(sizes)]
+    return Estimate(step, sf, sb, list(sizes), layers, max(ends), max(dp_costs), 0.0, max(opt_costs), mem, oom, num_mb, imb,
+                    {"send_time": max(send) if send else 0.0, "heterogeneous": 1.0})

@@ -81,6 +81,41 @@ def partition_dp(cost: Sequence[float], pp: int, layer_level: bool = False, comm
     return sizes[::-1]
 
 
+def partition_hetero(cost_by_stage: Sequence[Sequence[float]], layer_level: bool = False,
+                     comm: Optional[Sequence[float]] = None) -> List[int]:
+    """Minimise the maximum stage cost when stage ``s`` pays ``cost_by_stage[s][node]`` for a node (stages on
+    different GPU types): the same dynamic programme as :func:`partition_dp` with one prefix sum per stage."""
+    pp = len(cost_by_stage)
+    n = len(cost_by_stage[0])
+    cuts = [0] + _allowed_cuts(n, layer_level) + [n]
+    pre = [np.concatenate([[0.0], np.cumsum(c)]) for c in cost_by_stage]
+    INF = float("inf")
+    K = len(cuts)
+    best = [[INF] * K for _ in range(pp + 1)]
+    back = [[-1] * K for _ in range(pp + 1)]
+    best[0][0] = 0.0
+    for s in range(1, pp + 1):
+        ps = pre[s - 1]
+        for j in range(1, K):
+            for i in range(j):
+                if best[s - 1][i] == INF:
+                    continue
+                seg = ps[cuts[j]] - ps[cuts[i]]
+                if comm is not None and cuts[j] < n:
+                    seg += comm[cuts[j] - 1]
+                v = max(best[s - 1][i], seg)
+                if v < best[s][j]:
+                    best[s][j], back[s][j] = v, i
+    if best[pp][K - 1] == INF:
+        raise ValueError("no feasible partition")
+    sizes, j = [], K - 1
+    for s in range(pp, 0, -1):
+        i = back[s][j]
+        sizes.append(cuts[j] - cuts[i])
+        j = i
+    return sizes[::-1]
+
+
 def partition_minmax(cost: Sequence[float], pp: int, layer_level: bool = False, max_iter: int = 10000) -> List[int]:
     """Greedy boundary shifting: move one node (or one layer) across a stage boundary whenever that lowers the larger
     of the two stages it separates; stop when no boundary can be improved (or a state repeats)."""

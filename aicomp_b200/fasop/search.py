@@ -26,6 +26,8 @@ class FasopConfig:
     schedule: str = "1f1b"
     verbose: bool = False
     profile_dir: Optional[str] = None
+    pareto: bool = False              # mixed clusters: also evaluate every sub-cluster
+    placement: str = "permutations"   # mixed clusters: node orders to try ('permutations', 'cyclic', 'grouped')
 
 
 @dataclass
@@ -100,6 +102,38 @@ def evaluate(cfg: FasopConfig, model: ModelConfig, gpu: str, num_gpus: int, gbs:
     return out
 
 
+def evaluate_mixed(cfg: FasopConfig, model: ModelConfig, cluster: List[Tuple[str, int]], gbs: int, dbs: Dict[str, ProfileDB]
+                   ) -> List[SearchResult]:
+    """A cluster of several node types: every node order (device placement) x every (tp, dp, pp, mbs)."""
+    from .device_placement import node_orders, price_per_hour, stage_gpu_types
+    out: List[SearchResult] = []
+    n_nodes = sum(n for _, n in cluster)
+    num_gpus = n_nodes * cfg.gpu_per_node
+    iters = max(1, DATASETS.get(cfg.dataset, 131072) // gbs)
+    name = "+".join(f"{t}x{n * cfg.gpu_per_node}" for t, n in cluster)
+    seen = set()
+    for order in node_orders(cluster, cfg.placement):
+        price_h = price_per_hour(order, PRICE_PER_NODE_HOUR)
+        for tp, dp, pp, mbs in enumerate_parallel_strategies(num_gpus, gbs, model.num_layers, cfg.gpu_per_node):
+            if model.heads % tp or model.kv_heads % tp or model.ffn % tp:
+                continue
+            stages = stage_gpu_types(order, pp, dp, tp, cfg.gpu_per_node)
+            key = (tuple(stages), tp, dp, pp, mbs)
+            if key in seen:   # different node orders that give every stage the same GPU type are one layout
+                continue
+            seen.add(key)
+            try:
+                e = estimate(model, dbs[stages[0]], stages[0], tp, dp, pp, mbs, gbs, cfg.pp_partition_method, cfg.gpu_per_node,
+                             cfg.precision // 8, cfg.schedule, stage_gpus=stages, dbs=dbs)
+            except ValueError:
+                continue
+            price_step = price_h / 3600.0 * e.step_time
+            out.append(SearchResult(gbs, mbs, tp, dp, pp, "-".join(stages), name, e.partition, e.partition_layers, e.step_time,
+                                    gbs / e.step_time, price_step, e.is_oom, max(e.peak_mem_gb), iters, iters * e.step_time,
+                                    iters * price_step, e.num_mb))
+    return out
+
+
 def run_strategy_search(cfg: FasopConfig, jsonl_path: Optional[str] = None) -> List[SearchResult]:
     model = MODEL_CONFIGS[cfg.model_type]
     if cfg.seq_len:
@@ -108,6 +142,29 @@ def run_strategy_search(cfg: FasopConfig, jsonl_path: Optional[str] = None) -> L
     sink = open(jsonl_path, "w") if jsonl_path else None
     if sink:
         sink.write(json.dumps({"type": "meta", "model": cfg.model_type, "gpus": cfg.gpus, "gbs": cfg.gbs, "time": time.time()}) + "\n")
+    if len({g for g, n in cfg.gpus if n > 0}) > 1:
+        from .device_placement import cluster_subsets
+        for gpu, _ in cfg.gpus:
+            if gpu not in GPU_SPECS:
+                raise ValueError(f"unknown GPU type {gpu}; known: {sorted(GPU_SPECS)}")
+        dbs = {g: ProfileDB(model, g, cfg.profile_dir) for g, _ in cfg.gpus}
+        for sub in cluster_subsets(cfg.gpus, cfg.pareto):
+            for gbs in cfg.gbs:
+                if len(sub) == 1:
+                    g, n = sub[0]
+                    rs = evaluate(cfg, model, g, n * cfg.gpu_per_node, gbs, dbs[g])
+                else:
+                    rs = evaluate_mixed(cfg, model, sub, gbs, dbs)
+                results.extend(rs)
+                if sink:
+                    for r in rs:
+                        sink.write(json.dumps(asdict(r)) + "\n")
+        if sink:
+            sink.close()
+        results.sort(key=lambda r: (r.is_oom, r.total_time))
+        for i, r in enumerate(results):
+            r.rank = i + 1
+        return results
     for gpu, nodes in cfg.gpus:
         if gpu not in GPU_SPECS:
             raise ValueError(f"unknown GPU type {gpu}; known: {sorted(GPU_SPECS)}")

@@ -106,3 +106,24 @@ def test_viewer_serves_page_and_data(tmp_path):
         assert data["meta"]["model"] == "llama3b" and len(data["rows"]) > 20
     finally:
         srv.shutdown()
+
+
+def test_device_placement_and_heterogeneous_search():
+    """Mixed clusters: node orders are distinct multiset permutations, a stage spanning two node types runs at the
+    slower one, and the search prefers putting more layers on the faster GPUs."""
+    from aicomp_b200.fasop.device_placement import cluster_subsets, node_orders, stage_gpu_types
+    from aicomp_b200.fasop.search import FasopConfig, run_strategy_search
+    orders = node_orders([("B200", 1), ("A100", 2)])
+    assert sorted(orders) == sorted({("B200", "A100", "A100"), ("A100", "B200", "A100"), ("A100", "A100", "B200")})
+    assert len(node_orders([("B200", 2), ("A100", 2)], "cyclic")) == 4
+    assert node_orders([("B200", 3)]) == [("B200", "B200", "B200")]
+    assert len(cluster_subsets([("B200", 1), ("A100", 2)], pareto=True)) == 5
+    assert stage_gpu_types(("B200", "A100"), pp=2, dp=8, tp=1, gpus_per_node=8) == ["B200", "A100"]
+    assert stage_gpu_types(("B200", "A100"), pp=1, dp=16, tp=1, gpus_per_node=8) == ["A100"]  # spans both: slower type
+    assert stage_gpu_types(("A100", "B200"), pp=4, dp=4, tp=1, gpus_per_node=8) == ["A100", "A100", "B200", "B200"]
+    res = run_strategy_search(FasopConfig([("B200", 1), ("A100", 1)], "llama3b", gbs=[64], pareto=True))
+    assert res and any("-" in r.node_type for r in res) and any(r.gpu_cluster == "B200x8" for r in res)
+    mixed = [r for r in res if r.node_type == "B200-A100" and r.pp == 2 and not r.is_oom]
+    assert mixed, "no two-stage layout with one stage per node type"
+    best = min(mixed, key=lambda r: r.step_time)
+    assert best.partition[0] > best.partition[1], best.partition  # the B200 stage takes more nodes than the A100 stage
