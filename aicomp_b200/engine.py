@@ -169,10 +169,9 @@ class Optimus_p:
         self.label_group = None
 
         self._user_loss_fn = loss_fn
-        # CUDA-graph replay of a stage's per-micro-batch forward/backward.  Tensor-parallel stages are replayed only
-        # with the NCCL collectives (which capture); the fused kernels' peer-flag epochs advance on the host.
-        self.cuda_graphs = (bool(cuda_graphs) and self.use_gpu and (tp_size == 1 or tp_backend == "nccl")
-                            and not activation_ckpt and not preserve_output)
+        # CUDA-graph replay of a stage's per-micro-batch forward/backward.  Tensor-parallel stages replay too: NCCL
+        # collectives capture, and the fused kernels keep their peer-flag epochs in device memory.
+        self.cuda_graphs = bool(cuda_graphs) and self.use_gpu and not activation_ckpt and not preserve_output
         self._graphed = None
         self._graph_sig = None
         if checkpoint:

@@ -52,6 +52,7 @@ struct GemmArgs {
   int tile_rotate;                 // M-tile order starts here (local rows first for AG, remote rows first for RS)
   const uint32_t* ready_flags;     // [MAX_PARTS] epochs written by the owners of the A parts (may be null)
   uint32_t ready_epoch;
+  const uint32_t* ready_epoch_ptr; // when set, the epoch is read from device memory (launches replayed from a CUDA graph)
   // ---- all-gather by push, inside this kernel: warp 6 of every CTA copies a slice of this rank's A shard into every
   // peer's gather buffer (plain stores over NVLink); the CTA that finishes last raises this rank's flag on all peers.
   const uint4* push_src;           // this rank's shard (null: no push)
@@ -172,7 +173,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmMaps maps, GemmArgs p) {
           a_part = m0 / p.a_part_rows;
           a_y = m0 - a_part * p.a_part_rows;
           if (p.ready_flags && !((ready_mask >> a_part) & 1u)) {
-            if (!wait_ready_flag(p.ready_flags + a_part, p.ready_epoch, p.err, &cta_abort)) { ok = false; break; }
+            const uint32_t want = p.ready_epoch_ptr ? *p.ready_epoch_ptr : p.ready_epoch;
+            if (!wait_ready_flag(p.ready_flags + a_part, want, p.err, &cta_abort)) { ok = false; break; }
             asm volatile("fence.proxy.async;" ::: "memory");
             ready_mask |= 1u << a_part;
           }
@@ -265,7 +267,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ GemmMaps maps, GemmArgs p) {
           __threadfence_system();
           for (int r = 0; r < p.push_world; ++r)
             if (r != p.push_rank)
-              asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.push_flag[r]), "r"(p.ready_epoch) : "memory");
+              asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.push_flag[r]),
+                           "r"(p.ready_epoch_ptr ? *p.ready_epoch_ptr : p.ready_epoch) : "memory");
         }
       }
     }
@@ -490,6 +493,7 @@ static int gemm_dispatch(const void* const* A_parts, int a_parts, int a_part_row
   p.tile_rotate = tile_rotate;
   p.ready_flags = ready_flags;
   p.ready_epoch = ready_epoch;
+  p.ready_epoch_ptr = push_cfg ? push_cfg->ready_epoch_ptr : nullptr;
   p.push_src = nullptr;
   p.push_n16 = 0;
   p.push_counter = nullptr;
@@ -561,15 +565,16 @@ extern "C" int b200_gemm_bf16_parts(const void* const* A_parts, int a_parts, int
 //               once the owner of each part has raised flag_ptrs[rank][slot][owner] to `epoch`;
 //   counter     device uint32 (zero), used to find the last CTA.
 // Tiles of the local rows are computed first, so the math starts while remote rows are still in flight.
-extern "C" int b200_ag_gemm_bf16(const void* x_local, void* const* gather_ptrs, void* const* flag_ptrs, int rank, int world, int slot,
-                                 unsigned int epoch, void* counter, const void* B, void* C, int T, int N, int K, long long ldb,
-                                 long long ldc, int b_mn, int* err, cudaStream_t stream) {
+static int ag_gemm_impl(const void* x_local, void* const* gather_ptrs, void* const* flag_ptrs, int rank, int world, int slot,
+                        unsigned int epoch, const uint32_t* epoch_ptr, void* counter, const void* B, void* C, int T, int N, int K,
+                        long long ldb, long long ldc, int b_mn, int* err, cudaStream_t stream) {
   using namespace b200;
   if (world < 1 || world > GEMM_MAX_PARTS || T % world) return -14;
   const int Tl = T / world;
   const long long shard_bytes = static_cast<long long>(Tl) * K * 2;
   if (shard_bytes % 16) return -10;
   GemmArgs cfg;
+  cfg.ready_epoch_ptr = epoch_ptr;
   cfg.push_src = static_cast<const uint4*>(x_local);
   cfg.push_n16 = shard_bytes / 16;
   cfg.push_counter = static_cast<unsigned int*>(counter);
@@ -587,4 +592,18 @@ extern "C" int b200_ag_gemm_bf16(const void* x_local, void* const* gather_ptrs, 
   const uint32_t* ready = static_cast<const uint32_t*>(flag_ptrs[rank]) + slot * 8;
   return gemm_dispatch(a_parts, world, Tl, B, c_parts, 1, 0, nullptr, T, N, K, K, ldb, ldc, 0, b_mn, 0, 1.0f, 0, 0, 1, rank * (Tl / GEMM_BM),
                        ready, epoch, err, stream, &cfg);
+}
+extern "C" int b200_ag_gemm_bf16(const void* x_local, void* const* gather_ptrs, void* const* flag_ptrs, int rank, int world, int slot,
+                                 unsigned int epoch, void* counter, const void* B, void* C, int T, int N, int K, long long ldb,
+                                 long long ldc, int b_mn, int* err, cudaStream_t stream) {
+  return ag_gemm_impl(x_local, gather_ptrs, flag_ptrs, rank, world, slot, epoch, nullptr, counter, B, C, T, N, K, ldb, ldc, b_mn, err,
+                      stream);
+}
+// Same, with the epoch read from device memory at run time (`epoch_ptr`, bumped by b200_epoch_bump earlier in the
+// stream): the launch can be captured in a CUDA graph and replayed.
+extern "C" int b200_ag_gemm_bf16_dev(const void* x_local, void* const* gather_ptrs, void* const* flag_ptrs, int rank, int world,
+                                     int slot, const void* epoch_ptr, void* counter, const void* B, void* C, int T, int N, int K,
+                                     long long ldb, long long ldc, int b_mn, int* err, cudaStream_t stream) {
+  return ag_gemm_impl(x_local, gather_ptrs, flag_ptrs, rank, world, slot, 0, static_cast<const uint32_t*>(epoch_ptr), counter, B, C, T,
+                      N, K, ldb, ldc, b_mn, err, stream);
 }

@@ -73,6 +73,19 @@ __global__ void wait_kernel(const uint32_t* my_flags, int world, int slot, uint3
   if (t < world) wait_flag(my_flags + slot * MAX_PEERS + t, epoch, err);
 }
 
+// Epochs kept in device memory: a launch sequence that bumps, signals and waits through these entry points contains no
+// host-side counter and can be captured in a CUDA graph and replayed (every rank replays the same sequence).
+__global__ void bump_epoch_kernel(uint32_t* e) { *e += 1u; }
+__global__ void signal_dev_kernel(PeerPtrs flags, int rank, int world, int slot, const uint32_t* epoch) {
+  __threadfence_system();
+  const int t = threadIdx.x;
+  if (t < world) st_release_sys(static_cast<uint32_t*>(flags.p[t]) + slot * MAX_PEERS + rank, *epoch);
+}
+__global__ void wait_dev_kernel(const uint32_t* my_flags, int world, int slot, const uint32_t* epoch, int* err) {
+  const int t = threadIdx.x;
+  if (t < world) wait_flag(my_flags + slot * MAX_PEERS + t, *epoch, err);
+}
+
 // ---------------------------------------------------------------- gradient all-reduce (mean)
 // Phase 1: rank r owns elements [r*chunk, (r+1)*chunk) and writes the scaled sum of all peers' values there.
 // Every CTA first waits (bounded) until all peers have signalled that their gradients are final.
@@ -196,6 +209,20 @@ static PeerPtrs to_peers(void* const* ptrs, int world) {
   return pp;
 }
 
+extern "C" int b200_epoch_bump(void* epoch, cudaStream_t stream) {
+  bump_epoch_kernel<<<1, 1, 0, stream>>>(static_cast<uint32_t*>(epoch));
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+extern "C" int b200_signal_dev(void* const* flag_ptrs, int rank, int world, int slot, const void* epoch, cudaStream_t stream) {
+  if (world > MAX_PEERS) return -10;
+  signal_dev_kernel<<<1, 32, 0, stream>>>(to_peers(flag_ptrs, world), rank, world, slot, static_cast<const uint32_t*>(epoch));
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+extern "C" int b200_wait_dev(const void* my_flags, int world, int slot, const void* epoch, int* err, cudaStream_t stream) {
+  if (world > MAX_PEERS) return -10;
+  wait_dev_kernel<<<1, 32, 0, stream>>>(static_cast<const uint32_t*>(my_flags), world, slot, static_cast<const uint32_t*>(epoch), err);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
 extern "C" int b200_signal(void* const* flag_ptrs, int rank, int world, int slot, unsigned int epoch, cudaStream_t stream) {
   if (world > MAX_PEERS) return -10;
   signal_kernel<<<1, 32, 0, stream>>>(to_peers(flag_ptrs, world), rank, world, slot, epoch);

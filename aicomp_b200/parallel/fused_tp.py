@@ -32,6 +32,11 @@ _lib.OPTIONAL_PROTOS.update({
     "b200_sum_parts_bf16": [P, _lib.I, _lib.L, P, _lib.L, P],
     "b200_ag_gemm_bf16": [P, ctypes.POINTER(P), ctypes.POINTER(P), _lib.I, _lib.I, _lib.I, ctypes.c_uint, P, P, P, _lib.I, _lib.I, _lib.I,
                           _lib.L, _lib.L, _lib.I, P, P],
+    "b200_ag_gemm_bf16_dev": [P, ctypes.POINTER(P), ctypes.POINTER(P), _lib.I, _lib.I, _lib.I, P, P, P, P, _lib.I, _lib.I, _lib.I,
+                              _lib.L, _lib.L, _lib.I, P, P],
+    "b200_epoch_bump": [P, P],
+    "b200_signal_dev": [ctypes.POINTER(P), _lib.I, _lib.I, _lib.I, P, P],
+    "b200_wait_dev": [P, _lib.I, _lib.I, P, P, P],
 })
 _lib.rebind()
 
@@ -50,9 +55,26 @@ class TPContext:
         self.rs_bufs = [None, None]
         self.ag_calls = 0
         self.rs_calls = 0
-        self.ag_epoch = [0, 0]
-        self.rs_epoch = [0, 0]
         self.counter = None
+        # One epoch per flag slot, in DEVICE memory: it is bumped, published and waited for by kernels in stream
+        # order, so a captured sequence of these launches replays correctly (no host-side counter is baked in).
+        self.epochs = torch.zeros(64, dtype=torch.int32, device=device)
+
+    def _eptr(self, slot: int) -> int:
+        return self.epochs.data_ptr() + 4 * slot
+
+    def bump(self, slot: int) -> None:
+        _lib.check_rc(_lib.require().b200_epoch_bump(self._eptr(slot), _lib.stream_ptr()), "epoch_bump")
+
+    def signal(self, slot: int, epoch_slot: int) -> None:
+        """Publish the current epoch of ``epoch_slot`` in flag ``slot`` of every peer."""
+        _lib.check_rc(_lib.require().b200_signal_dev(self.flags._ptrs, self.rank, self.size, slot, self._eptr(epoch_slot),
+                                                     _lib.stream_ptr()), "signal_dev")
+
+    def wait(self, slot: int, epoch_slot: int) -> None:
+        """Wait (bounded) until every peer's flag ``slot`` has reached the current epoch of ``epoch_slot``."""
+        _lib.check_rc(_lib.require().b200_wait_dev(self.flags.buf.ptrs[self.rank], self.size, slot, self._eptr(epoch_slot),
+                                                   _lib.err_word(self.device).data_ptr(), _lib.stream_ptr()), "wait_dev")
 
     def _buf(self, bufs, i: int, nbytes: int) -> SymmetricBuffer:
         b = bufs[i]
@@ -115,20 +137,20 @@ def _ag_gemm_raw(x_local: torch.Tensor, w: torch.Tensor, group, b_mn: bool = Fal
     i = ctx.ag_calls & 1
     ctx.ag_calls += 1
     buf = ctx._buf(ctx.ag_bufs, i, tp * Tl * K * 2)  # gather buffer: one slot per rank
-    # every peer has finished reading (its GEMM of two calls ago) what we are about to overwrite in its buffer
-    if ctx.ag_epoch[i]:
-        ctx.flags.wait(SLOT_AG_DONE + i, ctx.ag_epoch[i])
-    e = ctx.flags.next_epoch(SLOT_AG_READY + i)
-    ctx.ag_epoch[i] = e
+    # every peer has finished reading (its GEMM of two calls ago) what we are about to overwrite in its buffer: its
+    # "done" flag carries the epoch this buffer had then (all flags start at the initial epoch 0)
+    ctx.wait(SLOT_AG_DONE + i, SLOT_AG_READY + i)
+    ctx.bump(SLOT_AG_READY + i)
     if ctx.counter is None:
         ctx.counter = torch.zeros(4, dtype=torch.int32, device=x_local.device)
     out = torch.empty(Tl * tp, N, dtype=x_local.dtype, device=x_local.device)
-    rc = lib.b200_ag_gemm_bf16(x_local.data_ptr(), buf.ptr_array(), ctx.flags._ptrs, rank, tp, SLOT_AG_READY + i, e,
-                               ctx.counter.data_ptr(), w.data_ptr(), out.data_ptr(), Tl * tp, N, K, w.stride(0), out.stride(0),
-                               int(b_mn), _lib.err_word(x_local.device).data_ptr(), _lib.stream_ptr())
+    rc = lib.b200_ag_gemm_bf16_dev(x_local.data_ptr(), buf.ptr_array(), ctx.flags._ptrs, rank, tp, SLOT_AG_READY + i,
+                                   ctx._eptr(SLOT_AG_READY + i), ctx.counter.data_ptr(), w.data_ptr(), out.data_ptr(), Tl * tp, N, K,
+                                   w.stride(0), out.stride(0), int(b_mn), _lib.err_word(x_local.device).data_ptr(),
+                                   _lib.stream_ptr())
     _lib.check_rc(rc, "ag_gemm")
-    ctx.flags.signal(SLOT_AG_DONE + i, e)
-    ops._count(2)
+    ctx.signal(SLOT_AG_DONE + i, SLOT_AG_READY + i)
+    ops._count(4)
     return out
 
 
@@ -146,24 +168,22 @@ def _gemm_rs_raw(x: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False) ->
     ctx.rs_calls += 1
     slot_elems = Tl * N
     buf = ctx._buf(ctx.rs_bufs, j, tp * slot_elems * 2)
-    if ctx.rs_epoch[j]:  # owners have summed (and so finished reading) what we stored there two calls ago
-        ctx.flags.wait(SLOT_RS_DONE + j, ctx.rs_epoch[j])
-    e = ctx.flags.next_epoch(SLOT_RS_READY + j)
-    ctx.flags.epochs[SLOT_RS_DONE + j] = e
-    ctx.rs_epoch[j] = e
+    # owners have summed (and so finished reading) what we stored there two calls ago
+    ctx.wait(SLOT_RS_DONE + j, SLOT_RS_READY + j)
+    ctx.bump(SLOT_RS_READY + j)
     a_parts = (P * 1)(x.data_ptr())
     c_parts = (P * tp)(*[buf.ptrs[o] + rank * slot_elems * 2 for o in range(tp)])
     rot = ((rank + 1) % tp) * (Tl // 128)
     rc = lib.b200_gemm_bf16_parts(a_parts, 1, 0, w.data_ptr(), c_parts, tp, Tl, None, T, N, K, x.stride(0), w.stride(0), N,
                                   0, int(b_mn), 0, 1.0, 0, rot, None, 0, _lib.err_word(x.device).data_ptr(), _lib.stream_ptr())
     _lib.check_rc(rc, "gemm_rs")
-    ctx.flags.signal(SLOT_RS_READY + j, e)
-    ctx.flags.wait(SLOT_RS_READY + j, e)
+    ctx.signal(SLOT_RS_READY + j, SLOT_RS_READY + j)
+    ctx.wait(SLOT_RS_READY + j, SLOT_RS_READY + j)
     out = torch.empty(Tl, N, dtype=x.dtype, device=x.device)
     rc = lib.b200_sum_parts_bf16(buf.ptrs[rank], tp, slot_elems, out.data_ptr(), slot_elems, _lib.stream_ptr())
     _lib.check_rc(rc, "sum_parts")
-    ctx.flags.signal(SLOT_RS_DONE + j, e)
-    ops._count(5)
+    ctx.signal(SLOT_RS_DONE + j, SLOT_RS_READY + j)
+    ops._count(7)
     return out
 
 

@@ -23,10 +23,10 @@ REF = os.path.join(HERE, "_ref")
 
 
 def install() -> str:
-    src = "/root/reference/opt_prime/opt_prime"
+    src = os.path.join(os.environ.get("AICOMP_REFERENCE_TREE", ""), "opt_prime", "opt_prime")
     dst = os.path.join(REF, "opt_prime")
     if not os.path.isdir(src):
-        return "reference tree not mounted"
+        return "reference tree not mounted (set AICOMP_REFERENCE_TREE to its root)"
     os.makedirs(REF, exist_ok=True)
     if os.path.isdir(dst):
         shutil.rmtree(dst)

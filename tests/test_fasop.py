@@ -12,12 +12,8 @@ from aicomp_b200.fasop.sim1f1b import simulate, stage_order
 
 def _llama70b_10layer_costs():
     """The reference's solver benchmark case: A40 profile of llama70b, reduced to 10 layers (82 nodes), TP2, MBS4."""
-    import os
-    path = "/root/reference/fasop/known_cost/llama70b_A40_2.npz"
-    if os.path.exists(path):
-        row = np.load(path)["data"][2]
-    else:  # the published row (BASELINE table 2.3, tp 2 / mbs 4)
-        row = np.array([1.154, 3.619, 0.470, 0.571, 2.249, 7.135, 0.094, 5.451, 5.944, 53.149])
+    # the row the reference ships for tp 2 / mbs 4 (fasop/known_cost/llama70b_A40_2.npz), in ms
+    row = np.array([1.154, 3.619, 0.470, 0.571, 2.249, 7.135, 0.094, 5.451, 5.944, 53.149])
     seq = [0] + list(range(1, 9)) * 10 + [9]
     return np.array([row[i] for i in seq]) * 3.0
 

@@ -50,11 +50,14 @@ def test_tp2_training_fused_matches_nccl_backend():
     b = run_workers("train_worker", 2, dict(base, tp_backend="fused"), timeout=300, env_extra={"NCCL_NVLS_ENABLE": "0"})
     for x, y in zip(a[0]["losses"], b[0]["losses"]):
         assert abs(x - y) < 3e-2 * abs(x), (a[0]["losses"], b[0]["losses"])
-    # the NCCL collectives capture: the same stage replayed from CUDA graphs
-    c = run_workers("train_worker", 2, dict(base, tp_backend="nccl", graphs=True), timeout=300, env_extra={"NCCL_NVLS_ENABLE": "0"})
-    assert all(r["graphs"] for r in c), "capture fell back to eager"
-    for x, y in zip(a[0]["losses"], c[0]["losses"]):
-        assert abs(x - y) < 3e-2 * abs(x), (a[0]["losses"], c[0]["losses"])
+    # the same stage replayed from CUDA graphs: NCCL collectives capture, the fused kernels read their epochs from
+    # device memory
+    for be in ("nccl", "fused"):
+        c = run_workers("train_worker", 2, dict(base, tp_backend=be, graphs=True, steps=5), timeout=300,
+                        env_extra={"NCCL_NVLS_ENABLE": "0"})
+        assert all(r["graphs"] for r in c), f"{be}: capture fell back to eager"
+        for x, y in zip(a[0]["losses"], c[0]["losses"]):
+            assert abs(x - y) < 3e-2 * abs(x), (be, a[0]["losses"], c[0]["losses"])
 
 
 def test_pp2_peer_transport_and_graph_replay_match_nccl_eager():
