@@ -29,7 +29,9 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "library"],
+                    help="'library': the same engine with its kernels off - eager HF modules on cuBLAS / cuDNN SDPA / NCCL with "
+                         "fp32 parameters under bf16 autocast and torch.optim.AdamW, i.e. what the reference's stock path does")
     ap.add_argument("--layers", type=int, default=32, help="debug only: fewer layers make the result INVALID as a bench value")
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--seqs-per-gpu", type=int, default=8)
@@ -111,13 +113,19 @@ def run_ours(a):
         model = LlamaForCausalLM(cfg)
     seqs_per_replica = a.seqs_per_gpu * a.gpus // dp
     num_mb = seqs_per_replica  # micro-batch 1
-    eng = Optimus_p(model, num_mb=num_mb, use_gpu=True, pp_size=pp, dp_size=dp, tp_size=tp, dtype=torch.bfloat16,
-                    dp_backend=a.dp_backend, tp_backend=a.tp_backend, cuda_graphs=not a.no_graphs)
+    library = a.impl == "library"
+    if library:
+        eng = Optimus_p(model, num_mb=num_mb, use_gpu=True, pp_size=pp, dp_size=dp, tp_size=tp, dtype=torch.float32,
+                        fused_kernels=False, dp_backend="nccl", tp_backend="nccl", pp_backend="nccl", cuda_graphs=False)
+        opt = torch.optim.AdamW(eng.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
+    else:
+        eng = Optimus_p(model, num_mb=num_mb, use_gpu=True, pp_size=pp, dp_size=dp, tp_size=tp, dtype=torch.bfloat16,
+                        dp_backend=a.dp_backend, tp_backend=a.tp_backend, cuda_graphs=not a.no_graphs)
+        opt = FusedAdamW(eng.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1, grad_scale=1.0 / num_mb, max_grad_norm=1.0,
+                         norm_groups={"pp": eng.tpl.pp_group, "tp": eng.tpl.tp_group if tp > 1 else None})
     dev = eng.device
-    opt = FusedAdamW(eng.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1, grad_scale=1.0 / num_mb, max_grad_norm=1.0,
-                     norm_groups={"pp": eng.tpl.pp_group, "tp": eng.tpl.tp_group if tp > 1 else None})
     eng.optimizer = opt
-    if eng.dp is not None:
+    if eng.dp is not None and not library:
         opt.attach_to_reducer(eng.dp)
     S = a.seq
     gbs = a.seqs_per_gpu * a.gpus
@@ -132,7 +140,12 @@ def run_ours(a):
         ids = host_ids[i % n_batches].to(dev, non_blocking=True) if first else None
         labels = host_labels[i % n_batches].to(dev, non_blocking=True) if last else None  # labels go straight to the last stage
         opt.zero_grad()
-        eng.run(ids, labels, mode="1f1b")
+        if library:
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                eng.run(ids, labels, mode="1f1b")
+            eng.clip_grad_norm_(1.0)
+        else:
+            eng.run(ids, labels, mode="1f1b")
         opt.step()
         if last:
             loss_host.copy_(eng.get_loss_tensor().reshape(1), non_blocking=True)
@@ -184,10 +197,10 @@ def run_ours(a):
             "metric": "llama3_8b_train_tokens_per_s_per_box", "value": round(value, 1), "unit": "tokens/s", "n_gpus": a.gpus,
             "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms_step, 2), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
-            "impl": "ours",
+            "impl": "library stand-in (this engine, kernels off)" if library else "ours",
             "config": {"model": "Llama-3-8B" if a.layers == 32 else f"Llama-3-8B-width/{a.layers}L (INVALID: reduced)",
                        "global_batch": gbs, "seq_len": S, "micro_batch": 1, "num_microbatches": num_mb,
-                       "parallelism": f"pp{pp}xdp{dp}" + (f"xtp{tp}" if tp > 1 else ""), "schedule": "1f1b", "optimizer": "AdamW fp32 master + bf16 weights",
+                       "parallelism": f"pp{pp}xdp{dp}" + (f"xtp{tp}" if tp > 1 else ""), "schedule": "1f1b", "optimizer": "torch AdamW on fp32 parameters, bf16 autocast" if library else "AdamW fp32 master + bf16 weights",
                        "l2": "inputs larger than L2: every step streams >100 GB of weights, gradients and optimizer state"},
             "clocks": clocks,
             "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(2 * gbs * S * 8), "d2h_bytes_per_step": 4,
