@@ -87,3 +87,33 @@ def test_packed_dataset_serves_shifted_windows():
     assert x.shape == (16,) and (x[1:] == y[:-1]).all()
     bl = BlendedDataset([ds, ds], [0.7, 0.3], size=50)
     assert len(bl) == 50 and bl[49][0].shape == (16,)
+
+
+def test_schedule_in_flight_counts_and_ring_layout():
+    """Slots a stage needs for CUDA-graph replay (micro-batches between forward and backward) and the byte layout of
+    one pipeline mailbox slot."""
+    import torch
+
+    from aicomp_b200.parallel.schedule import Schedule1F1B, ScheduleGPipe
+
+    class _E:
+        training = True
+
+    def mk(cls, stage, P, M):
+        s = cls.__new__(cls)
+        s.e, s.stage, s.P, s.M = _E(), stage, P, M
+        return s
+    for P, M in ((2, 16), (4, 8), (4, 2), (1, 8)):
+        for stage in range(P):
+            s = mk(Schedule1F1B, stage, P, M)
+            live = peak = 0
+            for kind, _ in s.order():
+                live += 1 if kind == "F" else -1
+                peak = max(peak, live)
+            assert peak == s.in_flight() == min(P - stage, M)
+            assert mk(ScheduleGPipe, stage, P, M).in_flight() == M
+    from aicomp_b200.parallel.p2p import PeerChannel
+    ch = PeerChannel.__new__(PeerChannel)
+    total = ch._layout([(torch.bfloat16, (1, 2048, 4096), True), (torch.int64, (3,), False), (torch.float32, (5, 7), False)])
+    assert ch._offsets == [0, 2048 * 4096 * 2, 2048 * 4096 * 2 + 256]
+    assert total == 2048 * 4096 * 2 + 256 + 256 and all(o % 256 == 0 for o in ch._offsets)
