@@ -44,7 +44,10 @@ _UNKNOWN = object()
 # Non-``torch.nn`` classes kept as single ``call_module`` nodes: they own
 # buffers/parameters that are awkward as free ``get_attr`` nodes, and they are
 # the units the kernel rewrite pass swaps for fused sm_100a implementations.
-_DEFAULT_LEAF_SUFFIXES = ("RotaryEmbedding", "RMSNorm", "Conv1D")
+# "SparseMoeBlock": expert routing is data-dependent control flow (index lists per expert); the block is kept as one
+# module call, which is also the unit the hierarchical partitioner groups by.
+_DEFAULT_LEAF_SUFFIXES = ("RotaryEmbedding", "RMSNorm", "Conv1D", "SparseMoeBlock")
+_SHAPE_PRESERVING_SUFFIXES = ("SparseMoeBlock",)
 
 # Tensor factories do not dispatch through ``__torch_function__`` when only a
 # size/device argument is a Proxy, so they are wrapped while tracing.
@@ -53,13 +56,35 @@ _FACTORY_NAMES = (
     "randn", "rand", "randint", "finfo", "iinfo",
 )
 
-# Mask builders of ``transformers`` are replaced by ``None`` while tracing: the
-# causal structure is carried by ``is_causal`` of the attention op (the
-# reference's export path does the same, IR.py:1582-1613).
+# Mask builders of ``transformers`` are replaced while tracing (their vmap-based code cannot be traced).  With an
+# attention implementation that derives causality itself (sdpa, flash) they return ``None`` and the causal structure
+# is carried by ``is_causal`` of the attention op (the reference's export path does the same, IR.py:1582-1613).  The
+# ``eager`` implementation has no other source of causality than the mask, so there the causal builders return a
+# traceable additive mask ``[1, 1, q, q]`` built from ``arange`` comparisons on the embeddings' sequence length.
 _MASK_BUILDERS = (
     "create_causal_mask", "create_sliding_window_causal_mask", "create_chunked_causal_mask",
     "create_bidirectional_mask", "create_masks_for_generate",
 )
+_CAUSAL_BUILDERS = ("create_causal_mask", "create_sliding_window_causal_mask", "create_chunked_causal_mask")
+
+
+def _eager_causal_mask_builder(name: str):
+    def build(*args, **kwargs):
+        config = kwargs.get("config", args[0] if args else None)
+        embeds = kwargs.get("inputs_embeds", kwargs.get("input_embeds"))
+        if embeds is None:
+            embeds = next((a for a in args[1:] if isinstance(a, (Proxy, torch.Tensor))), None)
+        if embeds is None:
+            return None
+        q = embeds.shape[1]
+        idx = torch.arange(q, device=embeds.device)
+        keep = idx.unsqueeze(1) >= idx.unsqueeze(0)
+        window = getattr(config, "sliding_window", None) if name == "create_sliding_window_causal_mask" else None
+        if window:
+            keep = keep & ((idx.unsqueeze(1) - idx.unsqueeze(0)) < window)
+        mask = torch.zeros((q, q), dtype=embeds.dtype, device=embeds.device).masked_fill(~keep, torch.finfo(embeds.dtype).min)
+        return mask.unsqueeze(0).unsqueeze(0)
+    return build
 
 
 def _has_proxy(obj: Any) -> bool:
@@ -105,6 +130,12 @@ class MetaProxy(Proxy):
     def __getattr__(self, k):
         if k.startswith("__") and k.endswith("__"):
             raise AttributeError(k)
+        if k in ("dtype", "ndim"):
+            # static properties of a tensor: hand out the concrete value (``torch.finfo(x.dtype)``, ``x.ndim == 3``
+            # must work on it), as the HF tracer does; shapes and devices stay symbolic
+            v = self.node.meta.get("val", _UNKNOWN)
+            if isinstance(v, torch.Tensor):
+                return getattr(v, k)
         return MetaAttribute(self, k)
 
     def __len__(self):
@@ -244,8 +275,17 @@ class MetaTracer(fx.Tracer):
                 mod = self.root.get_submodule(self._strip_prefix + target if self._strip_prefix else target)
                 state = {n: _to_meta(p) for n, p in list(mod.named_parameters()) + list(mod.named_buffers())}
                 was_training = mod.training
-                out = torch.func.functional_call(mod, state, margs, mkwargs)
-                mod.train(was_training)
+                try:
+                    out = torch.func.functional_call(mod, state, margs, mkwargs)
+                except Exception:
+                    # data-dependent routing cannot run on meta tensors; such blocks map the residual stream to a
+                    # tensor of the same shape and dtype
+                    first = next((a for a in margs if isinstance(a, torch.Tensor)), None)
+                    if first is None or not type(mod).__name__.endswith(_SHAPE_PRESERVING_SUFFIXES):
+                        raise
+                    out = torch.empty_like(first)
+                finally:
+                    mod.train(was_training)
             elif kind == "get_attr":
                 obj = self.root
                 for part in (self._strip_prefix + target).split("."):
@@ -323,9 +363,10 @@ def _patched(tracer: MetaTracer, model: nn.Module, extra_patches: Dict[Tuple[Any
             pymod = sys.modules.get(modname)
             if pymod is None:
                 continue
+            eager = getattr(getattr(model, "config", None), "_attn_implementation", None) == "eager"
             for fn in _MASK_BUILDERS:
                 if hasattr(pymod, fn):
-                    patch(pymod, fn, lambda *a, **k: None)
+                    patch(pymod, fn, _eager_causal_mask_builder(fn) if eager and fn in _CAUSAL_BUILDERS else (lambda *a, **k: None))
         for (obj, name), new in extra_patches.items():
             patch(obj, name, new)
         yield
