@@ -85,3 +85,31 @@ def test_family_traces_and_splits_exactly(name):
     p0 = {n for n, _ in extract_stage(tr.gm, assign, plan, 0).named_parameters()}
     p1 = {n for n, _ in extract_stage(tr.gm, assign, plan, 1).named_parameters()}
     assert p0 and p1
+
+
+@pytest.mark.parametrize("name", ["vit", "whisper", "gpt2cls", "qwenmoe"])
+def test_family_trains_through_the_engine(name):
+    """Image, speech (two inputs), classification-head and mixture-of-experts models step through ``Optimus_p`` and
+    learn (single process, two micro-batches)."""
+    from aicomp_b200 import Optimus_p
+    torch.manual_seed(0)
+    model, kind = _tiny(name)
+    kw = {}
+    if kind == "ids":
+        data = torch.randint(1, 128, (4, 16))
+        labels = torch.randint(0, 3, (4,)) if name == "gpt2cls" else data.clone()
+    elif kind == "pixels":
+        data, labels = torch.randn(4, 3, 32, 32), torch.randint(0, 10, (4,))
+    else:
+        data = {"input_features": torch.randn(4, 8, 32), "decoder_input_ids": torch.randint(1, 128, (4, 8))}
+        labels = torch.randint(1, 128, (4, 8))
+        kw = {"input_names": ["input_features", "decoder_input_ids"]}
+    e = Optimus_p(model, num_mb=2, use_gpu=False, **kw)
+    opt = torch.optim.AdamW(e.parameters(), lr=1e-3)
+    losses = []
+    for _ in range(3):
+        opt.zero_grad()
+        e.run(data, labels, mode="1f1b")
+        opt.step()
+        losses.append(sum(e.get_loss()) / 2)
+    assert losses[-1] < losses[0], losses
