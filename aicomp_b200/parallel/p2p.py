@@ -20,7 +20,6 @@ The reference moves every tensor with NCCL ``isend``/``irecv`` (opt_prime/opt_pr
 """
 from __future__ import annotations
 
-import ctypes
 from typing import Any, List
 
 import torch
@@ -30,13 +29,7 @@ from ..ops import _lib
 from .comm import Channel, Comm, _decode, _encode, _same_signature
 from .symm import SymmetricBuffer
 
-P = ctypes.c_void_p
-_lib.OPTIONAL_PROTOS.update({
-    "b200_stream_store_flag": [P, ctypes.c_uint, P],
-    "b200_stream_wait_flag_geq": [P, ctypes.c_uint, P],
-    "b200_copy_async": [P, P, ctypes.c_longlong, P],
-})
-_lib.rebind()
+# the stream-flag and copy entry points are declared with the other symmetric-memory prototypes (parallel/symm.py)
 
 RING = 4          # slots per channel; flow control makes any value >= 1 correct
 _ALIGN = 256

@@ -31,6 +31,9 @@ _lib.OPTIONAL_PROTOS.update({
     "b200_reduce_scatter_mean_f32": [ctypes.POINTER(P), ctypes.POINTER(P), ctypes.c_int, ctypes.c_int, ctypes.c_longlong, ctypes.c_int,
                                      ctypes.c_uint, ctypes.c_int, P, P],
     "b200_peer_pull": [P, P, ctypes.c_longlong, ctypes.c_int, P],
+    "b200_stream_store_flag": [P, ctypes.c_uint, P],
+    "b200_stream_wait_flag_geq": [P, ctypes.c_uint, P],
+    "b200_copy_async": [P, P, ctypes.c_longlong, P],
     "b200_kv_push": [P, P, P, P, ctypes.c_int, ctypes.c_int, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_int, P, ctypes.c_uint,
                      P, P],
 })

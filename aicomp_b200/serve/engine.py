@@ -53,6 +53,12 @@ class ServingEngine:
                 num_pages = max(64, int(free * kv_memory_fraction) // page_bytes)
             else:
                 num_pages = 512
+            if tp_size > 1 and self.tpl.tp_group is not None:
+                # every rank of the replica must see the same pool size: admission decisions depend on it
+                import torch.distributed as dist
+                n = torch.tensor([num_pages], dtype=torch.int64, device=self.device)
+                dist.all_reduce(n, op=dist.ReduceOp.MIN, group=self.tpl.tp_group)
+                num_pages = int(n.item())
         first = min(l.layer_idx for l in self.layers)
         self.cache = PagedKVCache(len(self.layers), l0.hkv, l0.head_dim, num_pages, max_seqs, self.max_blocks, dtype, self.device,
                                   pool=pool, layer_offset=first, q_heads=l0.hq)
@@ -183,13 +189,26 @@ class ServingEngine:
         def now():
             return time.perf_counter() - t0 + skew
 
+        def group_now():
+            """The clock every scheduling decision uses: the first tensor-parallel rank's, broadcast to the group, so
+            that all ranks of a replica admit the same requests in the same step (their own clocks differ by
+            microseconds, which is enough to split a batch differently and mismatch the collectives)."""
+            t = now()
+            if self.tpl.tp_size > 1 and self.tpl.tp_group is not None:
+                import torch.distributed as dist
+                buf = torch.tensor([t], dtype=torch.float64, device=self.device)
+                dist.broadcast(buf, src=self.tpl.tp_ranks()[0], group=self.tpl.tp_group)
+                t = float(buf.item())
+            return t
+
         while sch.has_work():
-            plan = sch.plan_step(now())
+            t_step = group_now()
+            plan = sch.plan_step(t_step)
             if not plan.prefill and not plan.decode:
                 nxt = sch.waiting[0].arrival_s if sch.waiting else None
                 if nxt is None:
                     break
-                wait = nxt - now()
+                wait = nxt - t_step
                 if wait > 0:
                     if realtime:
                         time.sleep(min(wait, 0.01))
@@ -202,7 +221,7 @@ class ServingEngine:
             if plan.decode:
                 toks = self.decode(plan.decode)
                 sch.after_decode(plan.decode, toks, now())
-            if max_wall_s is not None and time.perf_counter() - t0 > max_wall_s:
+            if max_wall_s is not None and t_step > max_wall_s:
                 break
         if self.device.type == "cuda":
             torch.cuda.synchronize()
