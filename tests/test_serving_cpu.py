@@ -80,3 +80,13 @@ def test_pd_disaggregated_protocol_matches_hf_greedy():
     assert dec.cache.alloc.available() == 6 and pre.cache.alloc.available() == 15
     assert all(r.t_first_token is not None and r.t_finished >= r.t_first_token for r in dw.finished)
     assert tr.bytes_pushed > 0
+
+
+def test_tensor_parallel_serving_keeps_ranks_in_step():
+    """A TP2 replica under real-time arrivals: both ranks take the same scheduling decisions (one broadcast clock), so
+    the run finishes and gives the tokens of the single-rank engine."""
+    from tests.dist_utils import run_workers
+    one = run_workers("serve_worker", 1, {"tp": 1}, timeout=240)
+    two = run_workers("serve_worker", 2, {"tp": 2}, timeout=240)
+    assert two[0]["tokens"] == two[1]["tokens"] == one[0]["tokens"]
+    assert two[0]["requests"] == 6 and two[0]["unfinished"] == 0
