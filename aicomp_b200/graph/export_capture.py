@@ -26,8 +26,8 @@ import torch
 import torch.fx as fx
 import torch.nn as nn
 
-from .tracer import (_DEFAULT_LEAF_SUFFIXES, _MASK_BUILDERS, MODEL_TYPE_HF, MODEL_TYPE_SYMBOLIC, MODEL_TYPE_VIT, TraceResult,
-                     _default_example, _infer_model_type)
+from .tracer import (_CAUSAL_BUILDERS, _DEFAULT_LEAF_SUFFIXES, _MASK_BUILDERS, MODEL_TYPE_HF, MODEL_TYPE_SYMBOLIC, MODEL_TYPE_VIT,
+                     TraceResult, _default_example, _eager_causal_mask_builder, _infer_model_type)
 
 __all__ = ["export_to_module_graph"]
 
@@ -206,10 +206,12 @@ def export_to_module_graph(model: nn.Module, input_names: Optional[Sequence[str]
             if pm is None or pm.__name__ in seen or pm.__name__.startswith("torch."):
                 continue
             seen.add(pm.__name__)
+            eager = getattr(getattr(model, "config", None), "_attn_implementation", None) == "eager"
             for fn in _MASK_BUILDERS:
                 if hasattr(pm, fn):
                     saved.append((pm, fn, getattr(pm, fn)))
-                    setattr(pm, fn, lambda *a, **k: None)
+                    # eager attention has no other source of causality than the mask: give it a traceable one
+                    setattr(pm, fn, _eager_causal_mask_builder(fn) if eager and fn in _CAUSAL_BUILDERS else (lambda *a, **k: None))
         positional = model_type == MODEL_TYPE_SYMBOLIC
         ep = torch.export.export(model, tuple(examples[n] for n in input_names) if positional else (),
                                  {} if positional else kwargs,

@@ -113,3 +113,26 @@ def test_family_trains_through_the_engine(name):
         opt.step()
         losses.append(sum(e.get_loss()) / 2)
     assert losses[-1] < losses[0], losses
+
+
+@pytest.mark.parametrize("name", ["gptneo", "gptj", "bert", "electra", "opt", "vit", "whisper", "gpt2cls", "qwenmoe", "mistral"])
+def test_family_export_capture_is_exact(name):
+    """The ``dynamo_capture=True`` path (torch.export + unflatten, rebuilt as a module-level graph) on the same families."""
+    from aicomp_b200.graph.export_capture import export_to_module_graph
+    torch.manual_seed(0)
+    model, kind = _tiny(name)
+    model.eval()
+    if kind == "ids":
+        ex = {"input_ids": torch.randint(1, 128, (2, 16))}
+    elif kind == "pixels":
+        ex = {"pixel_values": torch.randn(2, 3, 32, 32)}
+    else:
+        ex = {"input_features": torch.randn(2, 8, 32), "decoder_input_ids": torch.randint(1, 128, (2, 8))}
+    with torch.no_grad():
+        ref = model(**ex).logits
+    tr = export_to_module_graph(model, list(ex), example_inputs=ex)
+    with torch.no_grad():
+        assert torch.allclose(_logits(tr.gm(**ex)), ref, atol=1e-6)
+        if kind == "ids":
+            other = {"input_ids": torch.randint(1, 128, (3, 24))}
+            assert torch.allclose(_logits(tr.gm(**other)), model(**other).logits, atol=1e-6)
