@@ -30,8 +30,8 @@ import torch.nn.functional as F
 
 from . import ops
 from .graph import partition as _partition
-from .graph.split import StagePlan, build_stage_plan, extract_stage
-from .graph.tracer import MODEL_TYPE_HF, MODEL_TYPE_SYMBOLIC, MODEL_TYPE_VIT, trace_model
+from .graph.split import StagePlan
+from .graph.tracer import MODEL_TYPE_HF, MODEL_TYPE_VIT
 from .parallel.comm import Comm
 from .parallel.schedule import SCHEDULES
 from .parallel.topology import Topology

@@ -10,11 +10,11 @@ included.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Optional
 
 import numpy as np
 
-from .config import GPU_SPECS, LAYER_NODES, NODE_TYPES, ModelConfig
+from .config import GPU_SPECS, NODE_TYPES, ModelConfig
 from .partitioners import partition, partition_hetero, stage_costs
 from .profiledb import ProfileDB
 from .sim1f1b import simulate

@@ -10,7 +10,7 @@ Each returns the list of stage sizes (number of nodes per stage).
 from __future__ import annotations
 
 import itertools
-from typing import Callable, List, Optional, Sequence
+from typing import List, Optional, Sequence
 
 import numpy as np
 

@@ -15,7 +15,7 @@ import torch.nn as nn
 from ..utils.log import get_logger
 from . import partition as _partition
 from .split import StagePlan, build_stage_plan, extract_stage
-from .tracer import MODEL_TYPE_HF, trace_model
+from .tracer import trace_model
 
 log = get_logger(__name__)
 

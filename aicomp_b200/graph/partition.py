@@ -26,7 +26,7 @@ from __future__ import annotations
 
 import os
 import re
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Tuple
 
 import torch
 import torch.fx as fx

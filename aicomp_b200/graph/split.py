@@ -19,7 +19,7 @@ Module paths keep their dotted HF names inside the stage module, so a stage
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Dict, List
 
 import torch
 import torch.fx as fx

@@ -10,7 +10,6 @@ The paged, per-sequence cache used for serving lives in :mod:`aicomp_b200.serve.
 """
 from __future__ import annotations
 
-import math
 from typing import Dict, Optional, Tuple
 
 import torch

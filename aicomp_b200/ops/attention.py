@@ -14,7 +14,6 @@ from typing import Optional
 import torch
 import torch.nn.functional as F
 
-from . import _lib
 
 __all__ = ["causal_attention_packed", "attention_reference"]
 

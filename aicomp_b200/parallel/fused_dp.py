@@ -13,7 +13,6 @@ Baseline it replaces: torch DDP's bucketed NCCL all-reduce followed by a divide
 from __future__ import annotations
 
 import torch
-import torch.distributed as dist
 
 from .. import ops
 from ..ops import _lib

@@ -16,7 +16,7 @@ the input-gradient of one is the other, and the weight gradients gather their se
 from __future__ import annotations
 
 import ctypes
-from typing import Dict, Optional
+from typing import Dict
 
 import torch
 import torch.distributed as dist

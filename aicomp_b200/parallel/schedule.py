@@ -16,7 +16,7 @@ gradients for *every* differentiable tensor it received, not only the first.
 """
 from __future__ import annotations
 
-from typing import Any, Callable, Dict, List, Optional, Sequence
+from typing import Any, Dict, List, Optional
 
 import torch
 import torch.nn.functional as F

@@ -9,7 +9,6 @@ Conventions: activations are ``[B, S, H]``; sequence parallelism shards dim 1.
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 import torch.distributed as dist

@@ -11,7 +11,6 @@ from __future__ import annotations
 
 import gc
 import os
-from typing import Any, Dict
 
 import torch
 

@@ -36,7 +36,8 @@ def parse():
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--seqs-per-gpu", type=int, default=8)
     ap.add_argument("--dp-backend", default="fused")
-    ap.add_argument("--attn", default="auto")
+    ap.add_argument("--attn", default="kernel", choices=["kernel", "sdpa"],
+                    help="'sdpa': library attention (cuDNN) instead of the flash kernels of this framework, for an A/B comparison")
     ap.add_argument("--no-graphs", action="store_true", help="issue every kernel from Python instead of replaying CUDA graphs")
     ap.add_argument("--layout", default="", help="pp,dp,tp override, e.g. 2,1,4 with --seq 4096 --seqs-per-gpu 4 for the "
                                                  "TP4 x PP2 config (the metric line then names that parallelism)")
@@ -114,6 +115,9 @@ def run_ours(a):
     seqs_per_replica = a.seqs_per_gpu * a.gpus // dp
     num_mb = seqs_per_replica  # micro-batch 1
     library = a.impl == "library"
+    if a.attn == "sdpa":
+        from aicomp_b200.ops import flash
+        flash.TRAINING_USES_KERNEL = False
     if library:
         eng = Optimus_p(model, num_mb=num_mb, use_gpu=True, pp_size=pp, dp_size=dp, tp_size=tp, dtype=torch.float32,
                         fused_kernels=False, dp_backend="nccl", tp_backend="nccl", pp_backend="nccl", cuda_graphs=False)
