@@ -171,7 +171,7 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __rest
                      int V, long long ld, int ignore_index, float grad_scale, const float* __restrict__ grad_scale_dev,
                      int write_grad) {
   __shared__ float red_m[CE_THREADS / 32], red_s[CE_THREADS / 32];
-  __shared__ float sh_max, sh_lse;
+  __shared__ float sh_lse;
   const long long row = blockIdx.x;
   __nv_bfloat16* x = logits + row * ld;
   const long long label = labels[row];
@@ -204,7 +204,7 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __rest
     const float gm = warp_max(mm);
     ssum = (mm == -CUDART_INF_F) ? 0.f : ssum * __expf(mm - gm);
     ssum = warp_add(ssum);
-    if (l == 0) { sh_max = gm; sh_lse = gm + logf(ssum); }
+    if (l == 0) sh_lse = gm + logf(ssum);
   }
   __syncthreads();
   const float lse = sh_lse;
