@@ -58,6 +58,8 @@ def substitute_kernels(gm: fx.GraphModule, model: nn.Module, tp_size: int = 1, t
             new, kind = _llama.FusedLayerNorm(mod), "layernorm"
         elif type(mod) is nn.Linear:
             new, kind = _llama.FusedLinear(mod), "linear"
+        elif cname == "Conv1D" and hasattr(mod, "nf") and getattr(mod, "weight", None) is not None and mod.weight.dim() == 2:
+            new, kind = _llama.FusedConv1D(mod), "conv1d"
         elif type(mod) is nn.Embedding and mod.padding_idx is None and mod.max_norm is None:
             new, kind = _llama.FusedEmbedding(mod), "embedding"
         if new is not None:

@@ -327,6 +327,18 @@ class FusedLinear(nn.Module):
         return ops.linear(x, self.weight, self.bias)
 
 
+class FusedConv1D(nn.Module):
+    """HF ``Conv1D`` (GPT-2 family): a linear layer whose weight is stored ``[in, out]``; same parameters, tcgen05 GEMMs."""
+
+    def __init__(self, conv):
+        super().__init__()
+        self.weight, self.bias = conv.weight, conv.bias
+        self.nf = conv.nf
+
+    def forward(self, x):
+        return ops.linear_kn(x, self.weight, self.bias)
+
+
 class FusedEmbedding(nn.Module):
     def __init__(self, emb: nn.Embedding):
         super().__init__()

@@ -18,7 +18,7 @@ from . import _lib
 from ._lib import check_errors, have_gpu_kernels  # noqa: F401
 
 __all__ = [
-    "gemm", "linear", "rmsnorm", "layernorm", "rope_inplace", "apply_rope_qkv", "swiglu", "gelu_tanh", "cross_entropy",
+    "gemm", "linear", "linear_kn", "rmsnorm", "layernorm", "rope_inplace", "apply_rope_qkv", "swiglu", "gelu_tanh", "cross_entropy",
     "embedding", "scaled_softmax", "check_errors", "have_gpu_kernels", "kernels_for", "launch_count", "reset_launch_count", "add_launches",
 ]
 
@@ -169,6 +169,51 @@ class _LinearFn(torch.autograd.Function):
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0).to(dy.dtype)
         return dx, dw, db
+
+
+class _LinearKNFn(torch.autograd.Function):
+    """y = x W + b for a weight stored ``[in, out]`` (HF ``Conv1D`` of the GPT-2 family): the GEMM reads W as an
+    MN-major operand, so neither pass needs a transposed copy.  Same ``main_grad`` convention as :class:`_LinearFn`."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        x2 = _rows(x)
+        y = torch.empty(*x.shape[:-1], w.shape[1], dtype=x.dtype, device=x.device)
+        gemm(x2, w, b_mn=True, bias=bias, out=y.view(-1, w.shape[1]))
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.x_shape = x.shape
+        ctx.w_ref = w
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = _rows(dy)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty(ctx.x_shape, dtype=dy.dtype, device=dy.device)
+            gemm(dy2, w, out=dx.view(-1, w.shape[0]))             # dx[M, in] = dy[M, out] . W[in, out]^T
+        if ctx.needs_input_grad[1]:
+            mg = getattr(ctx.w_ref, "main_grad", None)
+            if mg is not None:
+                gemm(x2, dy2, a_mn=True, b_mn=True, out=mg, accumulate=True)   # dW[in, out] = x^T dy
+                ctx.w_ref.grad_accumulated = True
+            else:
+                dw = gemm(x2, dy2, a_mn=True, b_mn=True, out_dtype=w.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy.dtype)
+        return dx, dw, db
+
+
+def linear_kn(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ w + bias`` with ``w`` stored ``[in_features, out_features]``."""
+    if not kernels_for(x, w) or w.shape[0] % 8 or w.shape[1] % 8:
+        y = x.reshape(-1, x.shape[-1]) @ w
+        if bias is not None:
+            y = y + bias
+        return y.view(*x.shape[:-1], w.shape[1])
+    return _LinearKNFn.apply(x, w, bias)
 
 
 def _linear_small_m(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:

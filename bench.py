@@ -214,6 +214,8 @@ def run_ours(a):
         }
         print(json.dumps(res), flush=True)
     barrier()
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def run_reference(a):
