@@ -114,7 +114,9 @@ class Optimus_p:
         self.model_config = getattr(module, "config", None)
         self.model_class_name = type(module).__name__
         if fused_kernels is None:
-            fused_kernels = self.is_llama
+            # Llama gets the fused decoder layer; every other model gets its Linear / Conv1D / norm / embedding modules
+            # rewritten when it runs in bf16 on a GPU (the ops fall back to PyTorch for anything they do not cover)
+            fused_kernels = self.is_llama or (self.use_gpu and dtype == torch.bfloat16)
         self.fused_kernels = fused_kernels
 
         # ---- graph capture --------------------------------------------------
