@@ -23,6 +23,8 @@ def test_family_trains_in_bf16_on_the_kernels(name):
         data = {"input_features": torch.randn(8, 8, 32), "decoder_input_ids": torch.randint(1, 128, (8, 8))}
         labels = torch.randint(1, 128, (8, 8))
         kw = {"input_names": ["input_features", "decoder_input_ids"]}
+    data = {k: v.cuda() for k, v in data.items()} if isinstance(data, dict) else data.cuda()
+    labels = labels.cuda()
     before = ops.launch_count()
     e = Optimus_p(model, num_mb=2, use_gpu=True, dtype=torch.bfloat16, **kw)
     assert e.fused_kernels
