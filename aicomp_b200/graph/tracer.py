@@ -130,12 +130,13 @@ class MetaProxy(Proxy):
     def __getattr__(self, k):
         if k.startswith("__") and k.endswith("__"):
             raise AttributeError(k)
-        if k in ("dtype", "ndim"):
-            # static properties of a tensor: hand out the concrete value (``torch.finfo(x.dtype)``, ``x.ndim == 3``
-            # must work on it), as the HF tracer does; shapes and devices stay symbolic
+        if k == "ndim":
+            # the rank of a tensor is static: hand out the concrete value (``x.ndim == 3``).  ``dtype`` stays symbolic:
+            # a model is traced in fp32 and may run in bf16, so no dtype of the trace may be baked into the graph
+            # (``torch.finfo(x.dtype)`` is traced as a node, see the finfo / iinfo wrappers)
             v = self.node.meta.get("val", _UNKNOWN)
             if isinstance(v, torch.Tensor):
-                return getattr(v, k)
+                return v.ndim
         return MetaAttribute(self, k)
 
     def __len__(self):
@@ -351,8 +352,6 @@ def _patched(tracer: MetaTracer, model: nn.Module, extra_patches: Dict[Tuple[Any
 
     try:
         for n, orig in _FACTORY_ORIGINALS.items():
-            if n in ("finfo", "iinfo"):
-                continue
             patch(torch, n, _make_factory_wrapper(tracer, orig))
         seen = set()
         for sub in model.modules():

@@ -136,3 +136,21 @@ def test_family_export_capture_is_exact(name):
         if kind == "ids":
             other = {"input_ids": torch.randint(1, 128, (3, 24))}
             assert torch.allclose(_logits(tr.gm(**other)), model(**other).logits, atol=1e-6)
+
+
+@pytest.mark.parametrize("name", ["gptneo", "gptj", "bert", "opt", "gpt2cls", "mistral"])
+def test_traced_graph_carries_no_dtype_of_the_trace(name):
+    """Traced in fp32, run in bf16: a graph that had baked ``torch.float32`` (from ``x.dtype``, ``torch.finfo``) would fail
+    or silently up-cast; it must follow the parameters' dtype like the eager model."""
+    from aicomp_b200.graph.tracer import trace_model
+    torch.manual_seed(0)
+    model, _ = _tiny(name)
+    model.eval()
+    ex = {"input_ids": torch.randint(1, 128, (2, 16))}
+    tr = trace_model(model, ["input_ids"], example_inputs=ex)
+    model.to(torch.bfloat16)   # the graph module shares the model's parameters
+    with torch.no_grad():
+        got = _logits(tr.gm(**ex))
+        want = model(**ex).logits
+    assert got.dtype == want.dtype == torch.bfloat16
+    assert torch.allclose(got.float(), want.float(), atol=5e-2, rtol=5e-2)
