@@ -234,7 +234,7 @@ def _linear_small_m(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tenso
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    if not kernels_for(x, w):
+    if not kernels_for(x, w) or w.shape[0] % 8 or w.shape[1] % 8:   # e.g. a 10-class head: rows of C would not be 16-byte aligned
         return F.linear(x, w, bias)
     if not torch.is_grad_enabled() and x.numel() // x.shape[-1] <= 256:
         return _linear_small_m(x, w, bias)

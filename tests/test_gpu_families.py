@@ -23,7 +23,9 @@ def test_family_trains_in_bf16_on_the_kernels(name):
         data = {"input_features": torch.randn(8, 8, 32), "decoder_input_ids": torch.randint(1, 128, (8, 8))}
         labels = torch.randint(1, 128, (8, 8))
         kw = {"input_names": ["input_features", "decoder_input_ids"]}
-    data = {k: v.cuda() for k, v in data.items()} if isinstance(data, dict) else data.cuda()
+    def dev(t):  # floating-point inputs (pixels, audio features) in the model's dtype
+        return t.cuda().to(torch.bfloat16) if t.is_floating_point() else t.cuda()
+    data = {k: dev(v) for k, v in data.items()} if isinstance(data, dict) else dev(data)
     labels = labels.cuda()
     before = ops.launch_count()
     e = Optimus_p(model, num_mb=2, use_gpu=True, dtype=torch.bfloat16, **kw)
